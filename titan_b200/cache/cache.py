@@ -62,19 +62,27 @@ class SequenceCache:
         self.groups: List[CacheGroup] = []
         geometry = CacheGeometry(self.num_pages, page_size, max_slots, self.max_context, dtype, device)
         self.layer_place: List[Optional[Tuple[int, int]]] = []
-        by_key: Dict[tuple, List[int]] = {}
+        # A layer asks for one thing, for nothing, or (a mixer made of several mixers) for several things: entry (i, j) is
+        # the j-th need of layer i.
+        entries = []
         for i, need in enumerate(needs):
-            if need is not None:
-                by_key.setdefault(need.group_key(), []).append(i)
-        need_of = {need.group_key(): need for need in needs if need is not None}
-        place: Dict[int, Tuple[int, int]] = {}
-        for key, layers in by_key.items():
+            many = isinstance(need, (tuple, list))
+            for j, one in enumerate(need if many else (need,)):
+                if one is not None:
+                    entries.append(((i, j), one))
+        by_key: Dict[tuple, List[tuple]] = {}
+        for where, need in entries:
+            by_key.setdefault(need.group_key(), []).append(where)
+        need_of = {need.group_key(): need for _, need in entries}
+        place: Dict[tuple, Tuple[int, int]] = {}
+        for key, members in by_key.items():
             need = need_of[key]
-            g = build_cache_group(need, layers, geometry)
-            for j, layer in enumerate(layers):
-                place[layer] = (len(self.groups), j)
+            g = build_cache_group(need, [i for i, _ in members], geometry)
+            for index, where in enumerate(members):
+                place[where] = (len(self.groups), index)
             self.groups.append(g)
-        self.layer_place = [place.get(i) for i in range(len(needs))]
+        self.layer_place = [tuple(place.get((i, j)) for j in range(len(need))) if isinstance(need, (tuple, list)) else place.get((i, 0))
+                            for i, need in enumerate(needs)]
 
     # -- slots ---------------------------------------------------------- #
     def alloc_slot(self) -> int:
@@ -117,9 +125,15 @@ class SequenceCache:
 
     # -- views ----------------------------------------------------------- #
     def view_for_layer(self, layer: int):
+        """(group, index within the group) of the layer's storage; None if it asked for nothing; a tuple of such views, in
+        the order of its needs, if it asked for several things."""
         place = self.layer_place[layer]
         if place is None:
             return None
+        if place and not isinstance(place[0], int):
+            return tuple(None if p is None else (self.groups[p[0]], p[1]) for p in place)
+        if place == ():
+            return ()
         g = self.groups[place[0]]
         return g, place[1]
 

@@ -47,7 +47,7 @@ def _lookup(pairs, key, default):
 
 @dataclass(frozen=True)
 class MixerSpec:
-    kind: str                 # "attention" | "latent_attention" | "lightning"
+    kind: str                 # "attention" | "latent_attention" | "lightning" | "wkv" | "gated_delta" | "mlstm" | "parallel"
     hidden_size: int
     num_heads: int = 0
     num_kv_heads: int = 0
@@ -73,7 +73,7 @@ class MixerSpec:
 
 @dataclass(frozen=True)
 class FeedForwardSpec:
-    kind: str                 # "gated_mlp" | "moe" | "token_table"
+    kind: str                 # "gated_mlp" | "mlp" | "moe" | "token_table"
     hidden_size: int
     intermediate_size: int = 0
     activation: str = "silu"
@@ -97,7 +97,7 @@ class LayerSpec:
     feed-forward (None), or take more norms than two from ``norms`` (a norm after each part as well as
     before it, say) and its own constants from ``extra``."""
     index: int
-    arrangement: str          # "pre_norm" | "output_norm"
+    arrangement: str          # "pre_norm" | "pre_norm_scaled" | "output_norm" | "hyper"
     mixer: MixerSpec
     feed_forward: Optional[FeedForwardSpec]
     mixer_norm: Optional[NormSpec]
@@ -124,6 +124,8 @@ class ModelSpec:
     stop_token_ids: Tuple[int, ...] = ()
     embedding_scale: Optional[float] = None   # the embedded rows are multiplied by this (None: as stored)
     logit_scale: Optional[float] = None       # the logits are multiplied by this (None: as computed)
+    embedding_norm: Optional[NormSpec] = None  # a norm on the embedded rows, before the first layer (None: none)
+    streams: int = 1                          # copies of the residual stream that the blocks keep (the "hyper" arrangement); their sum leaves the last block
     # Tensors that no single layer owns (a table that every layer reads a slice of): (name, shape) pairs.  The model
     # loads each once and hands the dict to every part that has ``bind_shared``.
     shared_tensors: Tuple[Tuple[str, Tuple[int, ...]], ...] = ()
@@ -137,6 +139,8 @@ class ModelSpec:
         for i in self.order:
             if not 0 <= i < len(self.layers):
                 raise ConfigError(f"layer order names layer {i}, but there are {len(self.layers)} layers")
+        if self.streams < 1 or (self.streams > 1 and any(l.arrangement != "hyper" for l in self.layers)):
+            raise ConfigError(f"{self.streams} residual streams need every block to be of the 'hyper' arrangement")
         for layer in self.layers:
             src = layer.mixer.cache_from
             if src is None:

@@ -133,6 +133,8 @@ __global__ void __launch_bounds__(ATT_WARPS * 32) attn_prefill_kernel(AttnArgs a
     st.m = -FLT_MAX; st.l = 0.f;
 #pragma unroll
     for (int j = 0; j < MAXE; ++j) st.acc[j] = 0.f;
+    if (a.keep_first > 0 && lo > 0)                    // the kept first tokens that the window has left behind
+        attend_range<T, MAXE>(st, qs, a, 0, min(a.keep_first, lo), first_new, a.batch.q_start[seq], slot, h / (a.nh / a.nkv), lane);
     attend_range<T, MAXE>(st, qs, a, lo, pos + 1, first_new, a.batch.q_start[seq], slot, h / (a.nh / a.nkv), lane);
     if (a.sink) {                                     // one more term of the denominator, against the larger of the two maxima
         const float sk = a.sink[h], m_new = fmaxf(st.m, sk), alpha = expf(st.m - m_new);
@@ -170,6 +172,8 @@ __global__ void __launch_bounds__(ATT_WARPS * 32) attn_decode_kernel(AttnArgs a)
     const int slot = a.batch.slot_of_seq[b];
     const int wlo = a.window > 0 ? max(0, pos - a.window + 1) : 0;
     const int lo = max(wlo, split * keys), hi = min(len, (split + 1) * keys);
+    // the kept first tokens that lie in this split and before the window
+    const int klo = split * keys, khi = a.window > 0 ? min(min(a.keep_first, wlo), hi) : 0;
     float* qs = q_smem + warp * hd;
     for (int g = warp; g < group; g += ATT_WARPS) {
         const int h = (int)blockIdx.y * group + g;
@@ -178,10 +182,11 @@ __global__ void __launch_bounds__(ATT_WARPS * 32) attn_decode_kernel(AttnArgs a)
         st.m = -FLT_MAX; st.l = 0.f;
 #pragma unroll
         for (int j = 0; j < MAXE; ++j) st.acc[j] = 0.f;
-        if (lo < hi) {
+        if (lo < hi || klo < khi) {
             __syncwarp();
             load_query<T>(qs, (const T*)a.q + (size_t)b * a.q_stride + h * hd, hd, lane);
-            attend_range<T, MAXE>(st, qs, a, lo, hi, 0x7fffffff, 0, slot, kh, lane);
+            if (klo < khi) attend_range<T, MAXE>(st, qs, a, klo, khi, 0x7fffffff, 0, slot, kh, lane);
+            if (lo < hi) attend_range<T, MAXE>(st, qs, a, lo, hi, 0x7fffffff, 0, slot, kh, lane);
         }
 #pragma unroll
         for (int j = 0; j < MAXE; ++j) {
@@ -204,7 +209,7 @@ __global__ void attn_merge_kernel(AttnArgs a) {
     const float* part = a.scratch + (size_t)(b * a.nh + h) * a.n_splits * stride;
     const int len = a.batch.kv_len[b], keys = tb_split_keys(len, a.chunk, a.n_splits);
     const int used = min(a.n_splits, (len + keys - 1) / keys);
-    const int first = a.window > 0 ? max(0, len - a.window) / keys : 0;      // splits before the window's first key hold nothing
+    const int first = (a.window > 0 && a.keep_first <= 0) ? max(0, len - a.window) / keys : 0;      // splits before the window's first key hold nothing
     float m = -FLT_MAX;
     for (int s = first; s < used; ++s)
         if (part[s * stride + hd + 1] > 0.f) m = fmaxf(m, part[s * stride + hd]);
@@ -242,7 +247,7 @@ static int check_common(const AttnArgs& a, const char* who) {
     TB_REQUIRE(a.hd_v >= 0 && a.hd_v <= 32 * ATT_MAXE_WIDE, "%s: a value row of %d elements (at most %d)", who, a.hd_v, 32 * ATT_MAXE_WIDE);
     TB_REQUIRE(!a.v_alias || value_width(a) <= a.hd, "%s: a value that is the head of its key row cannot be wider (%d) than the key (%d)", who, value_width(a), a.hd);
     TB_REQUIRE(a.q_stride % 8 == 0 && a.kv_stride % 8 == 0, "%s: row strides must be multiples of 8 elements", who);
-    TB_REQUIRE(a.window >= 0, "%s: negative window", who);
+    TB_REQUIRE(a.window >= 0 && a.keep_first >= 0, "%s: negative window or kept tokens", who);
     TB_REQUIRE(!a.cache.storage || (a.cache.head_dim == a.hd && a.cache.kv_heads == a.nkv), "%s: the cache view does not match the heads", who);
     return 0;
 }

@@ -43,6 +43,9 @@ struct AttnArgs {
     // A sink in the softmax: sink[h] (float32, one per query head; null: none) joins the denominator of head h as one more
     // term exp(sink[h] - max), unscaled, without a key and without a value, once per query however the keys are split.
     const float* sink;
+    // With a window: the first keep_first positions of a sequence stay visible to every later query, at their true
+    // positions, beside the window's keys (0: the window alone).  The any-size kernels only.
+    int keep_first;
 };
 
 // How decode attention cuts the keys of ONE sequence into splits: ``chunk`` keys each while ``n_splits`` of

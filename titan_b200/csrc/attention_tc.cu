@@ -365,6 +365,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
 // TB_KV_FROM_CACHE (2): they are read from the cache's pages, where the step's own keys already lie (a cache
 // that keeps every key: no ring).
 extern "C" int tb_attn_prefill_tc_check(const AttnArgs* a, int dtype, int source) {
+    TB_REQUIRE(a->keep_first == 0 || a->window == 0, "attn_prefill_tc: a window that keeps a sequence's first tokens is not built here");
     TB_REQUIRE(dtype == TB_BF16, "attn_prefill_tc: bfloat16 only");
     TB_REQUIRE(source == TB_KV_FROM_STEP || source == TB_KV_FROM_CACHE, "attn_prefill_tc: a sequence continues from the cache and its keys are not all there");
     TB_REQUIRE(a->hd == HD, "attn_prefill_tc: head_dim %d is not %d", a->hd, HD);

@@ -161,7 +161,7 @@ __global__ void qk_norm_rope_kernel(QkArgs a) {
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
     const int t = blockIdx.x;
     const int head = blockIdx.y * nwarp + warp;
-    const bool touch_v = a.append || a.v_first || a.v_keep;
+    const bool touch_v = a.append || a.v_first || a.v_keep || a.v_norm_dims > 0;
     const int n_heads = a.nh + a.nkv + (touch_v ? a.nkv : 0);
     // cosine and sine of this token's angles, once per block: [rot/2] each, behind the warps' rows
     float* cs = head_smem + nwarp * a.hd;
@@ -203,11 +203,17 @@ __global__ void qk_norm_rope_kernel(QkArgs a) {
         const TOut* vf = a.v_first ? (const TOut*)a.v_first + (size_t)t * a.v_first_stride + vh * vf_head : nullptr;
         TOut* keep = a.v_keep ? (TOut*)a.v_keep + (size_t)t * a.v_keep_stride + vh * hd : nullptr;
         const float lam = vf ? *a.v_mix : 0.f;
+        float v_scale = 1.f;
+        if (a.v_norm_dims > 0) {                      // a value head of unit root mean square (elements beyond v_norm_dims are padding: zero)
+            ss = warp_sum(ss);
+            v_scale = 1.0f / sqrtf(ss / (float)a.v_norm_dims + a.v_eps);
+        }
 #pragma unroll
         for (int j = 0; j < QK_MAXE; ++j) {
             const int e = lane + 32 * j;
             if (e >= hd) continue;
-            const float val = vf ? (1.0f - lam) * v[j] + lam * (e < vf_head ? ldf(vf + e) : 0.f) : v[j];
+            const float own = v[j] * v_scale;
+            const float val = vf ? (1.0f - lam) * own + lam * (e < vf_head ? ldf(vf + e) : 0.f) : own;
             if (keep) stf(keep + e, val);
             if (dst) stf(dst + e, val);
         }
@@ -227,7 +233,6 @@ __global__ void qk_norm_rope_kernel(QkArgs a) {
         if (e < hd) y[e] = (normed && !a.norm_after) ? v[j] * scale * (w ? w[e] : 1.f) : v[j];
     }
     __syncwarp();
-    const int half = a.rope.rot >> 1;
     TOut* out = is_q ? (TOut*)a.q_out + (size_t)t * a.q_stride + head * hd
                      : (a.k_out ? (TOut*)a.k_out + (size_t)t * a.k_stride + (head - a.nh) * hd : nullptr);
     TOut* cdst = (is_k && to_cache)
@@ -239,10 +244,9 @@ __global__ void qk_norm_rope_kernel(QkArgs a) {
         const int e = lane + 32 * j;
         float r = e < hd ? y[e] : 0.f;
         if (e < hd && a.rope.inv_freq && e < a.rope.rot) {
-            const bool first = e < half;
-            const int k = first ? e : e - half;
-            const float s = sn[k], c = cs[k];
-            r = first ? y[e] * c - y[e + half] * s : y[e - half] * s + y[e] * c;
+            int k, partner; float sign;
+            tb_rotary_pair(a.rope, e, &k, &partner, &sign);
+            r = y[e] * cs[k] + sign * y[partner] * sn[k];
         }
         turned[j] = r;
         ss_after += r * r;
@@ -455,7 +459,7 @@ extern "C" int tb_qk_norm_rope(const QkArgs* args, int in_dtype, int out_dtype, 
     TB_REQUIRE(a.T > 0 && a.nh > 0 && a.nkv >= 0, "qk_norm_rope: sizes must be positive");
     TB_REQUIRE(a.hd > 0 && a.hd <= 32 * QK_MAXE, "qk_norm_rope: head_dim %d is not in 1..%d", a.hd, 32 * QK_MAXE);
     TB_REQUIRE(a.rope.rot >= 0 && a.rope.rot <= a.hd && a.rope.rot % 2 == 0, "qk_norm_rope: rotary_dim %d must be even and <= head_dim %d", a.rope.rot, a.hd);
-    TB_REQUIRE(!a.rope.adjacent, "qk_norm_rope: this kernel pairs dimension k with k + rot/2 only");
+    TB_REQUIRE(a.v_norm_dims >= 0 && a.v_norm_dims <= a.hd, "qk_norm_rope: a mean over %d of a value head's %d elements", a.v_norm_dims, a.hd);
     TB_REQUIRE(!a.zero_in || (a.append && a.in != a.q_out && a.k_out == nullptr),
                "qk_norm_rope: zeroing the input needs every head to be read (append) and outputs elsewhere");
     TB_REQUIRE(!a.row_sumsq || (a.row_width > 0 && a.row_parts > 0 && a.T <= 32), "qk_norm_rope: row sums of squares need the rows' width, their number of parts and at most 32 rows");
@@ -466,8 +470,8 @@ extern "C" int tb_qk_norm_rope(const QkArgs* args, int in_dtype, int out_dtype, 
     TB_REQUIRE(!(a.v_first || a.v_keep) || a.nkv > 0, "qk_norm_rope: values are blended or kept only where the rows have V heads");
     TB_REQUIRE(!(a.zero_in && a.v_keep && in_dtype == out_dtype), "qk_norm_rope: V rows kept in place cannot be zeroed as well");
     const int warps = 4;
-    const bool plain_heads = a.norm_dims == 0 && !a.norm_after && !a.v_first && !a.v_keep;     // what the vector kernel knows
-    const int n_heads = a.nh + a.nkv + ((a.append || a.v_first || a.v_keep) ? a.nkv : 0);
+    const bool plain_heads = a.norm_dims == 0 && !a.norm_after && !a.v_first && !a.v_keep && !a.v_norm_dims && !a.rope.adjacent;     // what the vector kernel knows
+    const int n_heads = a.nh + a.nkv + ((a.append || a.v_first || a.v_keep || a.v_norm_dims > 0) ? a.nkv : 0);
     dim3 grid(a.T, (n_heads + warps - 1) / warps);
     const size_t smem = ((size_t)warps * a.hd + a.rope.rot) * sizeof(float);
     const int in_bytes = in_dtype == TB_F32 ? 4 : 2, out_bytes = out_dtype == TB_F32 ? 4 : 2;

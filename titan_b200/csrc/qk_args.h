@@ -50,4 +50,7 @@ struct QkArgs {
     // Width of a head in the rows of v_first (0: hd): the layer that kept them may pad its heads to another width than this
     // one; elements beyond the narrower of the two are padding (zero) on both sides.
     int v_first_head;
+    // A unit norm of every V head without a weight: v_norm_dims > 0 divides a value head by the root mean square over its
+    // first v_norm_dims elements (eps v_eps inside the root) before it goes to the cache, to v_keep or into a blend.
+    int v_norm_dims; float v_eps;
 };

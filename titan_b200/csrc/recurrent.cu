@@ -1,0 +1,292 @@
+// Two recurrences over a matrix state S [dk][dv] per (sequence, head), float32, kept in the cache's state group:
+//
+//   the gated delta rule     S <- g S;  u = beta (v - S^T k);  S <- S + k u^T;  o = S^T q
+//                            (one decay g and one write strength beta per head and token; q and k unit vectors)
+//   the mLSTM matrix memory  m' = max(f + m, i);  S <- e^(f + m - m') S + e^(i - m') k v^T;  n likewise with k alone;
+//                            o = S^T q / (max(|n . q|, e^(-m')) + 1e-6)
+//                            (i and f the logarithms of an input and a forget gate; m a running maximum that starts at 0)
+//
+// tb_delta_prep   what lies between the delta rule's projections and its recurrence, one block a token: a short causal
+//                 convolution over time of every q, k and v channel (the inputs before the step come from the sequence's
+//                 state, which starts as zeros) with silu; q and k heads made unit vectors, q times dk^(-1/2); beta =
+//                 sigmoid(.) and g = exp(-exp(A_log) softplus(. + dt_bias)) per head.  All float32, results float32.
+// tb_recurrent_scan   either recurrence, tokens of a sequence in order whatever the step brings (a prompt, a piece of it,
+//                 one token): a block owns 32 value columns of one head's state, four neighbouring lanes share a column
+//                 (a quarter of its rows in registers each) and add their parts with two shuffles.  Sixteen tokens are
+//                 staged in shared memory at a time.  For the delta rule the block of the first head and first columns
+//                 also moves the convolution's window on: the last taps - 1 inputs of the sequence become its state.
+#include "common.cuh"
+
+struct DeltaPrepArgs {
+    const void* proj; int stride;           // [T][stride], compute dtype: q (G*dk) | k (G*dk) | v (H*dv) | ...
+    const float* taps; int n_taps;          // [C][n_taps], C = 2 G dk + H dv; the last column is the current token's
+    const float* state; long long state_stride; int conv_off;   // per slot: ... | at conv_off: [n_taps - 1][C] inputs, oldest first
+    const float* ba; int ba_stride;         // [T][>= 2H] float32: the projections for beta (H), then for the decay (H)
+    const float* a_log; const float* dt_bias;   // [H]
+    float* qkv; int qkv_stride;             // [T][C] float32 out: q | k | v as the recurrence takes them
+    float* gates; int gates_stride;         // [T][2H] float32 out: decay g (H), then beta (H)
+    const int* seq_of; const int* q_start; const int* slot_of_seq;
+    int T; int H; int G; int dk; int dv;
+};
+
+struct ScanArgs {
+    const void* q; int q_stride;            // rows of q heads side by side (dk each); a value head h reads q head h / group
+    const void* k; int k_stride;
+    const void* v; int v_stride;            // rows of H value heads (dv each)
+    int group;                              // value heads that share a q / k head
+    const float* gates; int gates_stride;   // [T][2H] float32.  delta: g, then beta.  mLSTM: the input gate's, then the forget gate's projection
+    const float* i_bias; const float* f_bias; float cap;      // mLSTM: [H] each; gates are capped as cap * tanh(. / cap)
+    float q_scale;                          // q is multiplied by this on the way in
+    float* out; int out_stride;             // [T][H * dv] float32
+    float* state; long long state_stride;   // per slot: S [H][dk][dv]; mLSTM: then n [H][dk], then m [H]
+    const int* q_start; const int* slot_of_seq;
+    int B; int H; int dk; int dv;
+    // delta rule: the convolution's window (see DeltaPrepArgs), moved on by this kernel
+    const void* conv_in; int conv_stride; int conv_bf16; int conv_channels; int n_taps; int conv_off;
+};
+
+namespace {
+
+__device__ __forceinline__ float silu_r(float z) { return z / (1.0f + expf(-z)); }
+__device__ __forceinline__ float softplus_r(float z) { return fmaxf(z, 0.f) + log1pf(expf(-fabsf(z))); }
+__device__ __forceinline__ float logsigmoid_r(float z) { return fminf(z, 0.f) - log1pf(expf(-fabsf(z))); }
+
+template <typename T>
+__global__ void __launch_bounds__(256) delta_prep_kernel(DeltaPrepArgs a) {
+    pdl_launch_dependents();
+    pdl_wait();
+    extern __shared__ float act[];          // [C]
+    const int t = blockIdx.x, H = a.H, G = a.G, dk = a.dk, dv = a.dv, n = a.n_taps;
+    const int C = 2 * G * dk + H * dv;
+    const int seq = a.seq_of[t], first = a.q_start[seq], i = t - first;
+    const float* old = a.state + (size_t)a.slot_of_seq[seq] * a.state_stride + a.conv_off;
+    const T* proj = (const T*)a.proj;
+    for (int c = threadIdx.x; c < C; c += blockDim.x) {
+        float acc = 0.f;
+        for (int j = 0; j < n; ++j) {
+            const int idx = i - (n - 1) + j;          // which token of the step (negative: before it)
+            const float x = idx >= 0 ? ldf(proj + (size_t)(first + idx) * a.stride + c) : old[(size_t)(n - 1 + idx) * C + c];
+            acc = fmaf(a.taps[(size_t)c * n + j], x, acc);
+        }
+        act[c] = silu_r(acc);
+    }
+    __syncthreads();
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
+    float* out = a.qkv + (size_t)t * a.qkv_stride;
+    for (int head = warp; head < 2 * G; head += nwarp) {           // q heads, then k heads: unit vectors
+        const float* x = act + head * dk;
+        float ss = 0.f;
+        for (int e = lane; e < dk; e += 32) ss = fmaf(x[e], x[e], ss);
+        ss = warp_sum(ss);
+        const float r = (head < G ? 1.0f / sqrtf((float)dk) : 1.0f) / sqrtf(ss + 1e-6f);
+        for (int e = lane; e < dk; e += 32) out[head * dk + e] = x[e] * r;
+    }
+    for (int c = 2 * G * dk + threadIdx.x; c < C; c += blockDim.x) out[c] = act[c];
+    if (threadIdx.x < H) {
+        const int h = threadIdx.x;
+        const float* ba = a.ba + (size_t)t * a.ba_stride;
+        float* g = a.gates + (size_t)t * a.gates_stride;
+        g[h] = expf(-expf(a.a_log[h]) * softplus_r(ba[H + h] + a.dt_bias[h]));
+        g[H + h] = 1.0f / (1.0f + expf(-ba[h]));
+    }
+}
+
+#define SCAN_DELTA 0
+#define SCAN_MLSTM 1
+#define SCAN_CH 16
+
+template <typename TIN, int MODE, int R>
+__global__ void __launch_bounds__(128) recurrent_scan_kernel(ScanArgs a) {
+    pdl_launch_dependents();
+    pdl_wait();
+    extern __shared__ __align__(16) float sm[];
+    constexpr int DKP = 4 * (R + 4);                    // a q or k row in shared memory: four runs of R, each padded by 4
+    float* qs = sm;                                     // [SCAN_CH][DKP]
+    float* ks = qs + SCAN_CH * DKP;                     // [SCAN_CH][DKP]
+    float* vs = ks + SCAN_CH * DKP;                     // [SCAN_CH][32]
+    float* g0 = vs + SCAN_CH * 32;                      // [SCAN_CH]
+    float* g1 = g0 + SCAN_CH;                           // [SCAN_CH]
+    const int b = blockIdx.x, h = blockIdx.y, tid = threadIdx.x, s = tid & 3, col = tid >> 2, j = blockIdx.z * 32 + col;
+    const int dk = a.dk, dv = a.dv, H = a.H;
+    const int t0 = a.q_start[b], t1 = a.q_start[b + 1];
+    const bool live = j < dv;
+    float* slot_state = a.state + (size_t)a.slot_of_seq[b] * a.state_stride;
+    float* S_g = slot_state + ((size_t)h * dk) * dv + j;
+    float* n_g = slot_state + (size_t)H * dk * dv + (size_t)h * dk;
+    float* m_g = slot_state + (size_t)H * dk * dv + (size_t)H * dk + h;
+    float S[R], nn[MODE == SCAN_MLSTM ? R : 1];
+    float m = 0.f;
+#pragma unroll
+    for (int ii = 0; ii < R; ++ii) {
+        const int i = s * R + ii;
+        S[ii] = (live && i < dk) ? S_g[(size_t)i * dv] : 0.f;
+        if constexpr (MODE == SCAN_MLSTM) nn[ii] = i < dk ? n_g[i] : 0.f;
+    }
+    if constexpr (MODE == SCAN_MLSTM) m = *m_g;
+    const int qh = h / a.group;
+    const TIN* qb = (const TIN*)a.q + (size_t)qh * dk;
+    const TIN* kb = (const TIN*)a.k + (size_t)qh * dk;
+    const TIN* vb = (const TIN*)a.v + (size_t)h * dv + blockIdx.z * 32;
+    for (int e = tid; e < 2 * SCAN_CH * DKP; e += 128) sm[e] = 0.f;      // the padding is read as factors: zeros
+    for (int c0 = t0; c0 < t1; c0 += SCAN_CH) {
+        const int n = min(SCAN_CH, t1 - c0);
+        __syncthreads();                                // the chunk before has been read
+        for (int e = tid; e < n * dk; e += 128) {
+            const int tok = e / dk, i = e - tok * dk, at = tok * DKP + (i / R) * (R + 4) + (i % R);
+            qs[at] = ldf(qb + (size_t)(c0 + tok) * a.q_stride + i) * a.q_scale;
+            ks[at] = ldf(kb + (size_t)(c0 + tok) * a.k_stride + i);
+        }
+        for (int e = tid; e < n * 32; e += 128) {
+            const int tok = e >> 5, c = e & 31;
+            vs[e] = blockIdx.z * 32 + c < dv ? ldf(vb + (size_t)(c0 + tok) * a.v_stride + c) : 0.f;
+        }
+        if (tid < n) {
+            const float* g = a.gates + (size_t)(c0 + tid) * a.gates_stride;
+            if constexpr (MODE == SCAN_DELTA) {
+                g0[tid] = g[h]; g1[tid] = g[H + h];
+            } else {                                    // logarithms of the input gate and of the forget gate, capped
+                g1[tid] = a.cap * tanhf((g[h] + a.i_bias[h]) / a.cap);
+                g0[tid] = logsigmoid_r(a.cap * tanhf((g[H + h] + a.f_bias[h]) / a.cap));
+            }
+        }
+        __syncthreads();
+        for (int tt = 0; tt < n; ++tt) {
+            const float* qr = qs + tt * DKP + s * (R + 4);
+            const float* kr = ks + tt * DKP + s * (R + 4);
+            const float vj = vs[tt * 32 + col];
+            float acc = 0.f;
+            if constexpr (MODE == SCAN_DELTA) {
+                const float decay = g0[tt], beta = g1[tt];
+                float pred = 0.f;
+#pragma unroll
+                for (int ii = 0; ii < R; ++ii) {
+                    S[ii] *= decay;
+                    pred = fmaf(S[ii], kr[ii], pred);
+                }
+                pred += __shfl_xor_sync(0xffffffffu, pred, 1);
+                pred += __shfl_xor_sync(0xffffffffu, pred, 2);
+                const float u = beta * (vj - pred);
+#pragma unroll
+                for (int ii = 0; ii < R; ++ii) {
+                    S[ii] = fmaf(kr[ii], u, S[ii]);
+                    acc = fmaf(S[ii], qr[ii], acc);
+                }
+                acc += __shfl_xor_sync(0xffffffffu, acc, 1);
+                acc += __shfl_xor_sync(0xffffffffu, acc, 2);
+            } else {
+                const float f = g0[tt], i = g1[tt];
+                const float m_new = fmaxf(f + m, i), keep = expf(f + m - m_new), add = expf(i - m_new);
+                m = m_new;
+                float nq = 0.f;
+                const float av = add * vj;
+#pragma unroll
+                for (int ii = 0; ii < R; ++ii) {
+                    S[ii] = fmaf(keep, S[ii], kr[ii] * av);
+                    nn[ii] = fmaf(keep, nn[ii], add * kr[ii]);
+                    acc = fmaf(S[ii], qr[ii], acc);
+                    nq = fmaf(nn[ii], qr[ii], nq);
+                }
+                acc += __shfl_xor_sync(0xffffffffu, acc, 1);
+                acc += __shfl_xor_sync(0xffffffffu, acc, 2);
+                nq += __shfl_xor_sync(0xffffffffu, nq, 1);
+                nq += __shfl_xor_sync(0xffffffffu, nq, 2);
+                acc = acc / (fmaxf(fabsf(nq), expf(-m_new)) + 1e-6f);
+            }
+            if (s == 0 && live) a.out[(size_t)(c0 + tt) * a.out_stride + (size_t)h * dv + j] = acc;
+        }
+    }
+    if (live) {
+#pragma unroll
+        for (int ii = 0; ii < R; ++ii) {
+            const int i = s * R + ii;
+            if (i < dk) S_g[(size_t)i * dv] = S[ii];
+        }
+    }
+    if constexpr (MODE == SCAN_MLSTM) if (blockIdx.z == 0 && col == 0) {
+#pragma unroll
+        for (int ii = 0; ii < R; ++ii) {
+            const int i = s * R + ii;
+            if (i < dk) n_g[i] = nn[ii];
+        }
+        if (s == 0) *m_g = m;
+    }
+    if constexpr (MODE == SCAN_DELTA) if (a.conv_in && h == 0 && blockIdx.z == 0 && a.n_taps > 1) {
+        // The sequence's last n_taps - 1 inputs become the convolution's state: from the step's rows, or, where the step
+        // brought fewer, from the old state moved up.  A thread owns a channel and goes from the oldest row on, so that
+        // it reads every old row before it writes over it.
+        const int C = a.conv_channels, rows = a.n_taps - 1, L = t1 - t0;
+        float* st = slot_state + a.conv_off;
+        for (int c = tid; c < C; c += 128) {
+            for (int r = 0; r < rows; ++r) {
+                const int idx = L - rows + r;
+                float x;
+                if (idx >= 0) {
+                    const size_t at = (size_t)(t0 + idx) * a.conv_stride + c;
+                    x = a.conv_bf16 ? __bfloat162float(((const __nv_bfloat16*)a.conv_in)[at]) : ((const float*)a.conv_in)[at];
+                } else {
+                    x = st[(size_t)(r + L) * C + c];
+                }
+                st[(size_t)r * C + c] = x;
+            }
+        }
+    }
+}
+
+template <typename TIN, int MODE, int R>
+int launch_scan_r(const ScanArgs& a, cudaStream_t stream) {
+    constexpr size_t smem = (size_t)(2 * SCAN_CH * 4 * (R + 4) + SCAN_CH * 32 + 2 * SCAN_CH) * sizeof(float);
+    static_assert(smem <= 48 * 1024, "the staging area fits the default shared memory");
+    dim3 grid(a.B, a.H, (a.dv + 31) / 32);
+    tb_launch(recurrent_scan_kernel<TIN, MODE, R>, grid, dim3(128), smem, stream, a);
+    return 0;
+}
+
+template <typename TIN, int MODE>
+int launch_scan(const ScanArgs& a, cudaStream_t stream) {
+    const int rows = (a.dk + 3) / 4;
+    if (rows <= 8) return launch_scan_r<TIN, MODE, 8>(a, stream);
+    if (rows <= 16) return launch_scan_r<TIN, MODE, 16>(a, stream);
+    if (rows <= 32) return launch_scan_r<TIN, MODE, 32>(a, stream);
+    return launch_scan_r<TIN, MODE, 64>(a, stream);
+}
+
+}  // namespace
+
+extern "C" int tb_delta_prep(const DeltaPrepArgs* args, int dtype, cudaStream_t stream) {
+    DeltaPrepArgs a = *args;
+    TB_REQUIRE(a.T > 0 && a.H > 0 && a.G > 0 && a.H % a.G == 0 && a.dk > 0 && a.dv > 0, "delta_prep: sizes must be positive, heads a multiple of the key heads");
+    TB_REQUIRE(a.n_taps >= 1 && a.n_taps <= 64, "delta_prep: %d taps (1 to 64)", a.n_taps);
+    TB_REQUIRE(a.H <= 256, "delta_prep: %d heads (at most 256)", a.H);
+    TB_REQUIRE(a.proj && a.taps && a.state && a.ba && a.a_log && a.dt_bias && a.qkv && a.gates && a.seq_of && a.q_start && a.slot_of_seq, "delta_prep: missing buffers");
+    const int C = 2 * a.G * a.dk + a.H * a.dv;
+    TB_REQUIRE(a.stride >= C && a.qkv_stride >= C && a.ba_stride >= 2 * a.H && a.gates_stride >= 2 * a.H, "delta_prep: rows too short");
+    const size_t smem = (size_t)C * sizeof(float);
+    TB_REQUIRE(smem <= 48 * 1024, "delta_prep: %d channels (at most 12,288)", C);
+    if (dtype == TB_F32) tb_launch(delta_prep_kernel<float>, dim3(a.T), dim3(256), smem, stream, a);
+    else if (dtype == TB_BF16) tb_launch(delta_prep_kernel<__nv_bfloat16>, dim3(a.T), dim3(256), smem, stream, a);
+    else TB_REQUIRE(false, "delta_prep: unknown dtype %d", dtype);
+    TB_CHECK_LAUNCH("delta_prep");
+    return 0;
+}
+
+// mode 0: the gated delta rule (q, k, v float32); mode 1: the mLSTM memory (q, k, v in ``dtype``).
+extern "C" int tb_recurrent_scan(const ScanArgs* args, int mode, int dtype, cudaStream_t stream) {
+    ScanArgs a = *args;
+    TB_REQUIRE(a.B > 0 && a.H > 0 && a.dk > 0 && a.dv > 0 && a.group > 0 && a.H % a.group == 0, "recurrent_scan: sizes must be positive");
+    TB_REQUIRE(a.dk <= 256, "recurrent_scan: %d key dimensions a head (at most 256)", a.dk);
+    TB_REQUIRE(a.H <= 65535 && (a.dv + 31) / 32 <= 65535, "recurrent_scan: too many heads or value columns");
+    TB_REQUIRE(a.q && a.k && a.v && a.gates && a.out && a.state && a.q_start && a.slot_of_seq, "recurrent_scan: missing buffers");
+    TB_REQUIRE(dtype == TB_F32 || dtype == TB_BF16, "recurrent_scan: unknown dtype %d", dtype);
+    if (mode == SCAN_DELTA) {
+        TB_REQUIRE(dtype == TB_F32, "recurrent_scan: the delta rule takes float32 q, k and v");
+        TB_REQUIRE(!a.conv_in || (a.n_taps >= 1 && a.conv_channels > 0), "recurrent_scan: the convolution's window needs its sizes");
+        if (launch_scan<float, SCAN_DELTA>(a, stream)) return 1;
+    } else if (mode == SCAN_MLSTM) {
+        TB_REQUIRE(a.i_bias && a.f_bias && a.cap > 0.f, "recurrent_scan: the mLSTM gates need their biases and a positive cap");
+        if (dtype == TB_F32 ? launch_scan<float, SCAN_MLSTM>(a, stream) : launch_scan<__nv_bfloat16, SCAN_MLSTM>(a, stream)) return 1;
+    } else {
+        TB_REQUIRE(false, "recurrent_scan: unknown mode %d", mode);
+    }
+    TB_CHECK_LAUNCH("recurrent_scan");
+    return 0;
+}

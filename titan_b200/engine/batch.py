@@ -117,6 +117,7 @@ class StepContext:
     run: int = 0                       # which run of the layer order is at work (set by the model)
     next_block: object = None          # the block that runs after this one (None after the last): a block may prepare its input
     carried: Dict[object, object] = field(default_factory=dict)     # what parts hand on within THIS step (a cache owner's rows for its readers, ...)
+    after_layer: object = None         # callable(run, residual [T, H] float32) that the model calls after every run of a layer (None: nobody watches)
     after_blocks: List[object] = field(default_factory=list)        # callables the model runs once after the last block (appends that had to wait)
 
     def row_sums(self) -> Optional[torch.Tensor]:

@@ -64,6 +64,7 @@ class Engine:
         if not torch.cuda.is_available():
             raise RuntimeError("titan_b200 runs on a CUDA device (sm_100a); none is visible and there is no CPU path")
         self.options = options
+        self.layer_observer = None                # callable(run, residual rows) called after every run of a layer in eager steps (tests, debugging)
         self.device = torch.device(options.device)
         torch.cuda.set_device(self.device)
         K.lib()                                   # build / load the kernels now, loudly
@@ -140,7 +141,9 @@ class Engine:
 
     # -- the step function ---------------------------------------------------- #
     def _context(self, layout: StepLayout) -> StepContext:
-        return StepContext(layout, K.current_stream(), self.dtype, self.device, self.step_options, self.scratch)
+        ctx = StepContext(layout, K.current_stream(), self.dtype, self.device, self.step_options, self.scratch)
+        ctx.after_layer = self.layer_observer
+        return ctx
 
     def _check_entries(self, entries: Sequence[StepEntry]) -> List[int]:
         if not entries:

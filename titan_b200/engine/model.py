@@ -26,6 +26,7 @@ class DecoderModel:
         self.spec = spec
         self.blocks = [build_block(layer) for layer in spec.layers]
         self.final_norm = NORMS.build(spec.final_norm)
+        self.embedding_norm = None if spec.embedding_norm is None else NORMS.build(spec.embedding_norm)
         self.embedding: Optional[torch.Tensor] = None
         self.shared = {}
         self.lm_head: Optional[torch.Tensor] = None
@@ -52,6 +53,8 @@ class DecoderModel:
             if hasattr(b, "bind_shared"):
                 b.bind_shared(self.shared)
         self.final_norm.bind(get)
+        if self.embedding_norm is not None:
+            self.embedding_norm.bind(get)
         self.lm_head = self.embedding if self.spec.lm_head is None else get(self.spec.lm_head)
 
     def weight_bytes(self) -> int:
@@ -79,16 +82,39 @@ class DecoderModel:
         K.embed(self.embedding, lay.tokens, x, ctx.stream)
         if self.spec.embedding_scale is not None:
             K.scale_f32(x, float(self.spec.embedding_scale), ctx.stream)
+        if self.embedding_norm is not None:    # a norm on the embedded rows; the residual stream stays float32
+            x = self.embedding_norm.forward(x, ctx, out_dtype=torch.float32)
+        streams = self.spec.streams
+        if streams > 1:                        # every stream starts as the embedded rows: [T, streams * H], stream s at columns s * H
+            x = x.repeat(1, streams)
         if "row_sums" not in ctx.scratch:      # places where folded norms leave sums of squares: one per run of a layer
             ctx.scratch["row_sums"] = torch.zeros((len(self.spec.order), 16, 32), dtype=torch.float32, device=ctx.device)
         for run, i in enumerate(self.spec.order):
             ctx.run = run
             ctx.next_block = self.blocks[self.spec.order[run + 1]] if run + 1 < len(self.spec.order) else None
             self.blocks[i].forward(x, ctx, cache.view_for_layer(self.cache_run_of(run)))
+            if ctx.after_layer is not None:    # an observer of the residual stream after every run of a layer (tests, debugging)
+                ctx.after_layer(run, self._stream_sum(x, ctx, peek=True))
         for late in ctx.after_blocks:          # cache rows that a later layer of the step still had to read as they were
             late()
         ctx.after_blocks.clear()
-        return x
+        return self._stream_sum(x, ctx)
+
+    def _stream_sum(self, x: torch.Tensor, ctx, peek: bool = False) -> torch.Tensor:
+        """The residual stream that leaves the blocks: x itself, or the sum of the streams (which the last block may have
+        left in ``ctx.carried`` already)."""
+        streams = self.spec.streams
+        if streams == 1:
+            return x
+        kept = ctx.carried.get("stream_sum") if peek else ctx.carried.pop("stream_sum", None)
+        if kept is not None and kept[1] == ctx.run + 1:
+            return kept[0]
+        total = torch.empty((x.shape[0], self.spec.hidden_size), dtype=torch.float32, device=ctx.device)
+        ones = ctx.scratch.get("stream_ones")
+        if ones is None or ones.numel() != streams:
+            ones = ctx.scratch["stream_ones"] = torch.ones(streams, dtype=torch.float32, device=ctx.device)
+        K.hyper(x, streams, ctx.stream, in_w=ones, h=total)
+        return total
 
     def logits(self, x: torch.Tensor, ctx, rows: torch.Tensor) -> torch.Tensor:
         """float32 logits [len(rows), vocab] at the given rows of the residual stream."""

@@ -79,7 +79,7 @@ class QkArgs(Structure):
                 ("row_sumsq", c_void_p), ("row_parts", c_int), ("row_width", c_int), ("row_eps", c_float),
                 ("norm_dims", c_int), ("norm_after", c_int),
                 ("v_first", c_void_p), ("v_first_stride", c_int), ("v_mix", c_void_p), ("v_keep", c_void_p), ("v_keep_stride", c_int),
-                ("v_first_head", c_int)]
+                ("v_first_head", c_int), ("v_norm_dims", c_int), ("v_eps", c_float)]
 
 
 class AttnArgs(Structure):
@@ -88,7 +88,7 @@ class AttnArgs(Structure):
                 ("nh", c_int), ("nkv", c_int), ("hd", c_int), ("window", c_int), ("scale", c_float),
                 ("chunk", c_int), ("n_splits", c_int), ("scratch", c_void_p),
                 ("early_len", c_void_p), ("early_mode", c_int), ("fused_qk", POINTER(QkArgs)),
-                ("hd_v", c_int), ("v_alias", c_int), ("head_blocks", c_int), ("sink", c_void_p)]
+                ("hd_v", c_int), ("v_alias", c_int), ("head_blocks", c_int), ("sink", c_void_p), ("keep_first", c_int)]
 
 
 class LatentArgs(Structure):
@@ -125,6 +125,30 @@ class WkvArgs(Structure):
                 ("T", c_int), ("B", c_int), ("H", c_int), ("dk", c_int), ("W", c_int), ("rank", c_int), ("max_new", c_int)]
 
 
+class HyperArgs(Structure):
+    """Arguments of the kernel between two sublayers of a model with several residual streams (csrc/hyper.cu)."""
+    _fields_ = [("xs", c_void_p), ("S", c_int), ("W", c_int), ("rows", c_int), ("y", c_void_p), ("mix", c_void_p), ("out_w", c_void_p),
+                ("zero_y", c_int), ("in_w", c_void_p), ("norm_w", c_void_p), ("eps", c_float), ("h", c_void_p)]
+
+
+class DeltaPrepArgs(Structure):
+    """Arguments of the kernel between the delta-rule mixer's projections and its recurrence (csrc/recurrent.cu)."""
+    _fields_ = [("proj", c_void_p), ("stride", c_int), ("taps", c_void_p), ("n_taps", c_int), ("state", c_void_p), ("state_stride", c_longlong),
+                ("conv_off", c_int), ("ba", c_void_p), ("ba_stride", c_int), ("a_log", c_void_p), ("dt_bias", c_void_p),
+                ("qkv", c_void_p), ("qkv_stride", c_int), ("gates", c_void_p), ("gates_stride", c_int),
+                ("seq_of", c_void_p), ("q_start", c_void_p), ("slot_of_seq", c_void_p),
+                ("T", c_int), ("H", c_int), ("G", c_int), ("dk", c_int), ("dv", c_int)]
+
+
+class ScanArgs(Structure):
+    """Arguments of the recurrences over a matrix state: the gated delta rule and the mLSTM memory (csrc/recurrent.cu)."""
+    _fields_ = [("q", c_void_p), ("q_stride", c_int), ("k", c_void_p), ("k_stride", c_int), ("v", c_void_p), ("v_stride", c_int),
+                ("group", c_int), ("gates", c_void_p), ("gates_stride", c_int), ("i_bias", c_void_p), ("f_bias", c_void_p), ("cap", c_float),
+                ("q_scale", c_float), ("out", c_void_p), ("out_stride", c_int), ("state", c_void_p), ("state_stride", c_longlong),
+                ("q_start", c_void_p), ("slot_of_seq", c_void_p), ("B", c_int), ("H", c_int), ("dk", c_int), ("dv", c_int),
+                ("conv_in", c_void_p), ("conv_stride", c_int), ("conv_bf16", c_int), ("conv_channels", c_int), ("n_taps", c_int), ("conv_off", c_int)]
+
+
 class SampleArgs(Structure):
     _fields_ = [("logits", c_void_p), ("ld", c_int), ("V", c_int), ("B", c_int), ("slot_of_row", c_void_p),
                 ("temperature", c_void_p), ("top_k", c_void_p), ("top_p", c_void_p), ("penalty", c_void_p),
@@ -154,6 +178,13 @@ def lib():
         l.tb_dyt.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p]
         l.tb_scale_add.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]
         l.tb_wkv.argtypes = [POINTER(WkvArgs), c_int, c_int, c_void_p]
+        l.tb_hyper.argtypes = [POINTER(HyperArgs), c_int, c_void_p]
+        l.tb_polynorm.argtypes = [c_void_p, c_int, c_void_p, c_float, c_void_p, c_int, c_int, c_int, c_int, c_void_p]
+        l.tb_gate_rows.argtypes = [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p]
+        l.tb_head_norm_gate.argtypes = [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
+                                        c_float, c_float, c_void_p]
+        l.tb_delta_prep.argtypes = [POINTER(DeltaPrepArgs), c_int, c_void_p]
+        l.tb_recurrent_scan.argtypes = [POINTER(ScanArgs), c_int, c_int, c_void_p]
         l.tb_moe_route_all.argtypes = [c_void_p, c_int, c_int, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p]
         l.tb_gemm_simt_batched.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
                                            c_longlong, c_longlong, c_longlong, c_void_p]
@@ -372,6 +403,67 @@ def scale_add(y: torch.Tensor, scale: Optional[torch.Tensor], x: torch.Tensor, s
     w, b, alpha = norm if h is not None else (None, None, None)
     _check(lib().tb_scale_add(y.data_ptr(), _ptr(scale), x.data_ptr(), int(zero_y), _ptr(w), _ptr(b), _ptr(alpha), _ptr(h),
                               dtype_code(h.dtype) if h is not None else F32, x.shape[0], x.shape[1], stream))
+
+
+def hyper(xs: torch.Tensor, streams: int, stream: int, y: Optional[torch.Tensor] = None, mix: Optional[torch.Tensor] = None,
+          out_w: Optional[torch.Tensor] = None, zero_y: bool = True, in_w: Optional[torch.Tensor] = None,
+          norm_w: Optional[torch.Tensor] = None, eps: float = 0.0, h: Optional[torch.Tensor] = None) -> None:
+    """Between two sublayers of a model with ``streams`` residual streams, xs float32 [T, streams * W].  With ``y`` (float32 [T, W],
+    the sublayer's result): every stream r becomes sum_s mix[s, r] x_s + out_w[r] * y (``zero_y`` leaves y zeroed).  With ``in_w``:
+    h = the blend sum_r in_w[r] x_r of the new streams, RMS-normed with ``norm_w`` and ``eps`` into h's dtype, or, without a norm,
+    as it is in float32."""
+    _need_cuda(xs, y, mix, out_w, in_w, norm_w, h)
+    W = xs.shape[1] // streams
+    if xs.dtype != torch.float32 or not xs.is_contiguous() or xs.shape[1] != streams * W or (y is not None and (y.dtype != torch.float32 or not y.is_contiguous() or y.shape != (xs.shape[0], W))) \
+            or (h is not None and (not h.is_contiguous() or h.shape != (xs.shape[0], W))) or any(t is not None and t.dtype != torch.float32 for t in (mix, out_w, in_w, norm_w)):
+        raise KernelError("hyper: contiguous float32 rows of streams, a float32 result and float32 weights are wanted")
+    a = HyperArgs(xs.data_ptr(), streams, W, xs.shape[0], _ptr(y), _ptr(mix), _ptr(out_w), int(zero_y), _ptr(in_w), _ptr(norm_w), eps, _ptr(h))
+    _check(lib().tb_hyper(byref(a), dtype_code(h.dtype) if h is not None else F32, stream))
+
+
+def polynorm(z: torch.Tensor, coef: torch.Tensor, eps: float, y: torch.Tensor, stream: int) -> None:
+    """y = a N(z) + b N(z^2) + c N(z^3) + e row by row, N(x) = x / sqrt(mean(x^2) + eps), coef = (a, b, c, e) float32 on the device."""
+    _need_cuda(z, coef, y)
+    if z.dtype != y.dtype or z.shape != y.shape or z.stride(1) != 1 or y.stride(1) != 1 or coef.dtype != torch.float32 or coef.numel() != 4:
+        raise KernelError("polynorm: rows of one dtype and shape and four float32 coefficients are wanted")
+    _check(lib().tb_polynorm(z.data_ptr(), z.stride(0), coef.data_ptr(), eps, y.data_ptr(), y.stride(0), dtype_code(z.dtype), z.shape[0], z.shape[1], stream))
+
+
+GATE_SIGMOID, GATE_SILU = 0, 1
+
+
+def gate_rows(x: torch.Tensor, g: torch.Tensor, y: torch.Tensor, act: int, scale: float, stream: int) -> None:
+    """y = x * act(g) * scale, element by element (act GATE_SIGMOID or GATE_SILU, in float32); row-strided views of one dtype; y may be x."""
+    _need_cuda(x, g, y)
+    if len({x.dtype, g.dtype, y.dtype}) != 1 or x.shape != g.shape or x.shape != y.shape or x.stride(1) != 1 or g.stride(1) != 1 or y.stride(1) != 1:
+        raise KernelError("gate_rows: three views of one dtype and shape are wanted")
+    _check(lib().tb_gate_rows(x.data_ptr(), x.stride(0), g.data_ptr(), g.stride(0), y.data_ptr(), y.stride(0), dtype_code(x.dtype), x.shape[0], x.shape[1],
+                              int(act), float(scale), stream))
+
+
+def head_norm_gate(o: torch.Tensor, w: torch.Tensor, per_head: bool, g: torch.Tensor, y: torch.Tensor, heads: int, act: int, scale: float,
+                   eps: float, stream: int) -> None:
+    """Per head of dv = width / heads elements: y = o / sqrt(mean(o^2) + eps) * w * act(g) * scale.  o float32 [T, heads * dv]; w float32, one
+    row of dv for every head or (``per_head``) heads * dv; g and y in the compute dtype (row-strided views allowed)."""
+    _need_cuda(o, w, g, y)
+    dv = o.shape[1] // heads
+    if o.dtype != torch.float32 or w.dtype != torch.float32 or g.dtype != y.dtype or o.stride(1) != 1 or g.stride(1) != 1 or y.stride(1) != 1 \
+            or o.shape[1] != heads * dv or w.numel() != (heads * dv if per_head else dv) or g.shape != o.shape or y.shape != o.shape:
+        raise KernelError("head_norm_gate: float32 rows of whole heads, a gate and an output of one dtype")
+    _check(lib().tb_head_norm_gate(o.data_ptr(), o.stride(0), w.data_ptr(), dv if per_head else 0, g.data_ptr(), g.stride(0), y.data_ptr(), y.stride(0),
+                                   dtype_code(y.dtype), o.shape[0], heads, dv, int(act), float(scale), float(eps), stream))
+
+
+def delta_prep(args: "DeltaPrepArgs", dtype: torch.dtype, stream: int) -> None:
+    _check(lib().tb_delta_prep(byref(args), dtype_code(dtype), stream))
+
+
+SCAN_DELTA, SCAN_MLSTM = 0, 1
+
+
+def recurrent_scan(args: "ScanArgs", mode: int, dtype: torch.dtype, stream: int) -> None:
+    """The gated delta rule (SCAN_DELTA, float32 inputs) or the mLSTM memory (SCAN_MLSTM, inputs in ``dtype``) over a step's tokens."""
+    _check(lib().tb_recurrent_scan(byref(args), int(mode), dtype_code(dtype), stream))
 
 
 WKV_SHIFT, WKV_DECAY, WKV_SCAN, WKV_OUT = 0, 1, 2, 3

@@ -6,7 +6,7 @@ from typing import List
 from ..weights.loader import WeightSpec
 from .base import (BLOCKS, FEED_FORWARDS, MIXERS, NORMS, POSITIONS, FeedForward, Mixer, Norm, Part,
                    PositionEncoding, Registry)
-from . import attention, block, latent_attention, lightning, mlp, moe, norm, rotary, token_table, wkv  # noqa: F401  (registration)
+from . import attention, block, gated_delta, latent_attention, lightning, mlp, mlstm, moe, norm, parallel, rotary, token_table, wkv  # noqa: F401  (registration)
 
 
 def build_block(layer_spec):
@@ -22,6 +22,8 @@ def declare_weights(model_spec) -> List[WeightSpec]:
     specs += [WeightSpec(name, tuple(shape)) for name, shape in model_spec.shared_tensors]
     for layer in model_spec.layers:
         specs += build_block(layer).weight_specs()
+    if model_spec.embedding_norm is not None:
+        specs += NORMS.build(model_spec.embedding_norm).weight_specs("")
     specs += NORMS.build(model_spec.final_norm).weight_specs("")
     if model_spec.lm_head is not None:
         specs.append(WeightSpec(model_spec.lm_head, (model_spec.vocab_size, model_spec.hidden_size)))

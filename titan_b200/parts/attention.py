@@ -30,6 +30,14 @@ Options of the spec (``MixerSpec.extra``) beyond the common fields:
   root mean square (over the head's own width), without a weight, after or before the rotation.
 * ``sink``: name of a tensor with one number per query head that joins the softmax's denominator as exp(sink), with no
   key and no value, once.
+* ``value_norm``: an eps; every value head is divided by its root mean square (over the head's own width, without a
+  weight) before it goes to the cache, so the cache holds normed values.
+* ``keep_first`` (with ``window``): the first ``keep_first`` positions of a sequence stay visible to every later query beside
+  the window's keys, at their true positions.  The cache then keeps every key (no ring).
+* ``out_gate``: name of a [heads * value_dim, hidden] tensor; the concatenated heads are multiplied by sigmoid(W_g h), h the
+  mixer's own input, before the output projection.
+* ``output_scale``: a factor on what the mixer adds to the residual stream (a mixer that runs beside another); it is applied to
+  the rows that enter the output projection, in float32 before they are rounded.
 * ``value_mix`` = (first, name): values are blended across layers.  ``first`` None: this layer's values are what the
   others blend with, and it keeps them for the step; else v <- (1 - l) v + l v_first with l the tensor ``name`` and
   v_first the values of layer ``first`` for the same tokens.  The blended values are what the cache holds.
@@ -109,10 +117,16 @@ class AttentionMixer(Mixer):
             raise ValueError("a mixer that reads another layer's cache has no values to blend")
         # what the kernels that fold head norm, rotation and append into the attention do not know
         self.extended = bool(self.unit_norm or self.value_mix is not None or self.padded)
-        self.sink = self.mix_factor = None
+        self.value_norm = s.option("value_norm")         # None, or the eps of a unit norm of every value head
+        self.keep_first = int(s.option("keep_first", 0) or 0)
+        if self.keep_first < 0 or (self.keep_first and self.shared):
+            raise ValueError("keep_first is a count of positions, and a mixer that reads another layer's cache takes that layer's keys as they are")
+        self.gate_name = s.option("out_gate")
+        self.output_scale = float(s.option("output_scale", 1.0))
+        self.sink = self.mix_factor = self.w_gate = None
         self.position = POSITIONS.build(s.position)
-        if getattr(s.position, "pairing", "half") != "half" and s.position.kind == "rope":
-            raise ValueError("grouped-query attention rotates the pairs (k, k + rotary_dim/2) only")
+        adjacent = getattr(s.position, "pairing", "half") != "half" and s.position.kind == "rope"
+        self.extended = bool(self.extended or adjacent or self.value_norm is not None)
         self.scale = s.softmax_scale if s.softmax_scale is not None else 1.0 / math.sqrt(s.head_dim)
         if s.position.kind == "rope" and s.position.rotary_dim > self.key_dim:
             raise ValueError(f"{s.position.rotary_dim} rotated dimensions in a head of {self.key_dim}")
@@ -123,7 +137,8 @@ class AttentionMixer(Mixer):
     def cache_need(self) -> Optional[CacheNeed]:
         if self.shared:
             return None
-        return CacheNeed("kv", self.spec.num_kv_heads, self.hd, self.spec.window)
+        # kept first tokens stay in reach for good: such a window is a mask over a cache that keeps every key, not a ring
+        return CacheNeed("kv", self.spec.num_kv_heads, self.hd, None if self.keep_first else self.spec.window)
 
     def _names(self):
         """Tensor names (relative to the prefix) by role; "qkv" only if the spec names a fused tensor."""
@@ -149,6 +164,8 @@ class AttentionMixer(Mixer):
                           WeightSpec(p + n["v"], (s.num_kv_heads * vd, s.hidden_size))]
         if self.sink_name:
             specs.append(WeightSpec(p + self.sink_name, (s.num_heads,), "vector", ("normal", 1.0)))
+        if self.gate_name:
+            specs.append(WeightSpec(p + self.gate_name, (s.num_heads * vd, s.hidden_size)))
         if self.value_mix is not None and self.value_mix[0] is not None:      # (the layer the others blend with has no use for a factor)
             specs.append(WeightSpec(p + self.value_mix[1], (), "vector", ("normal", 0.3)))
         if s.qk_norm is not None:
@@ -172,6 +189,8 @@ class AttentionMixer(Mixer):
             self.w_o = torch.nn.functional.pad(w, (0, self.hd - self.value_dim)).reshape(s.hidden_size, self.Q).contiguous()
         if self.sink_name:
             self.sink = get(p + self.sink_name)
+        if self.gate_name:
+            self.w_gate = self._padded_rows(get(p + self.gate_name), s.num_heads, self.value_dim)
         if self.value_mix is not None and self.value_mix[0] is not None:
             self.mix_factor = get(p + self.value_mix[1]).reshape(1)
         if s.qk_norm is not None:
@@ -209,6 +228,8 @@ class AttentionMixer(Mixer):
         qa.eps = s.qk_norm.eps if s.qk_norm is not None else float(s.option("unit_norm_eps", 0.0))
         if self.unit_norm:
             qa.norm_dims, qa.norm_after = self.key_dim, int(self.unit_norm == "after_rotation")
+        if self.value_norm is not None and not self.shared:
+            qa.v_norm_dims, qa.v_eps = self.value_dim, float(self.value_norm)
         qa.nh, qa.nkv, qa.hd = s.num_heads, (0 if self.shared else s.num_kv_heads), hd
         qa.pos_of, qa.seq_of, qa.slot_of_seq = lay.pos_of.data_ptr(), lay.seq_of.data_ptr(), lay.slot_of_seq.data_ptr()
         qa.cache, qa.append, qa.T = view, int(append), T
@@ -278,6 +299,9 @@ class AttentionMixer(Mixer):
                 qa.v_first_head = kept.shape[1] // s.num_kv_heads
                 if not wide_sum:                               # the step's own V columns are what a prompt's attention reads
                     qa.v_keep, qa.v_keep_stride = qkv.data_ptr() + (Q + KV) * qkv.element_size(), width
+        if self.value_norm is not None and not self.shared and not wide_sum and not qa.v_keep:
+            # the normed values are what a prompt's attention reads: written back over the step's own V columns
+            qa.v_keep, qa.v_keep_stride = qkv.data_ptr() + (Q + KV) * qkv.element_size(), width
         folds_head_norm = wide_sum and ctx.options.get("fold_head_norm", True) and not self.extended
         if not folds_head_norm:
             K.qk_norm_rope(qa, qkv.dtype, q_buf.dtype, ctx.stream)
@@ -290,8 +314,9 @@ class AttentionMixer(Mixer):
         aa.nh, aa.nkv, aa.hd = s.num_heads, view.kv_heads, hd
         aa.window, aa.scale = s.window or 0, self.scale
         aa.sink = None if self.sink is None else self.sink.data_ptr()
+        aa.keep_first = self.keep_first if s.window else 0
         if decode:
-            fast = ctx.options.get("attention", "fast") != "plain" and q_buf.dtype == torch.bfloat16 and hd in (64, 128)
+            fast = ctx.options.get("attention", "fast") != "plain" and q_buf.dtype == torch.bfloat16 and hd in (64, 128) and not aa.keep_first
             chunk, splits = decode_split(lay, view.kv_heads, ctx.options, fast)
             need = lay.B * s.num_heads * splits * (hd + 2)
             scratch = ctx.scratch.get("attn_partials")
@@ -328,7 +353,7 @@ class AttentionMixer(Mixer):
                 source = K.KV_FROM_CACHE
             else:
                 source = K.KV_NOWHERE
-            if hd not in (64, 128):                       # the sizes the tensor-core kernels are built for: no other asks for (and compiles) them
+            if hd not in (64, 128) or aa.keep_first:      # what the tensor-core kernels are built for: nothing else asks for (and compiles) them
                 source = K.KV_NOWHERE
             if mode == "fast" and source and K.attn_prefill_tc_accepts(aa, q_buf.dtype, source):
                 K.attn_prefill_tc(aa, source, ctx.stream)
@@ -338,6 +363,12 @@ class AttentionMixer(Mixer):
                 K.attn_prefill(aa, q_buf.dtype, ctx.stream)
             if not self.shared and not append_now:
                 K.kv_append(qkv[:, Q:], view, lay.c_struct(), ctx.stream)
+        if self.w_gate is not None:                  # the heads times sigmoid(W_g h) (and the mixer's factor), in place
+            gate = ctx.empty((T, Q))
+            linear.matmul(rows_of(h), self.w_gate, gate, linear.EPI_STORE, ctx)
+            K.gate_rows(attn, gate, attn, K.GATE_SIGMOID, self.output_scale, ctx.stream)
+        elif self.output_scale != 1.0:
+            raise NotImplementedError("an output scale is applied with the output gate; a mixer without a gate has none")
         linear.matmul(attn, self.w_o, out, linear.EPI_ADD, ctx)
 
 

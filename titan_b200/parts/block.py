@@ -203,3 +203,114 @@ class OutputNormBlock(Part):
 
 
 BLOCKS.register("output_norm", OutputNormBlock)
+
+
+class HyperConnectionBlock(Part):
+    """``hyper``: a pre-norm block over several residual streams ("hyper-connections").  The model keeps S copies of the
+    residual stream side by side, [T, S * H].  For each sublayer, with three small tensors ``in`` [S], ``out`` [S] and
+    ``mix`` [S, S] (indexed [from, to]):
+
+        u = sum_s in[s] x_s;   y = sublayer(norm(u));   x_r <- sum_s mix[s, r] x_s + out[r] * y   (all r from the old streams)
+
+    The tensors' names are ``<name>.in|out|mix`` with one name per sublayer in ``LayerSpec.extra["connections"]``; the number
+    of streams is ``LayerSpec.extra["streams"]``.  The feed-forward, with its norm and connection, may be absent.  A sublayer
+    adds into a zeroed float32 buffer of the step; ONE kernel then writes it into the streams, mixes them, leaves the buffer
+    zeroed and reads the blend for the sublayer that follows, normed (the feed-forward's input here, or the next block's
+    mixer input, which that block finds in ``ctx.carried``; after the last block the plain sum of the streams, which the
+    model takes as the residual stream that goes to the final norm)."""
+
+    def __init__(self, spec):
+        if spec.mixer_norm is None or (spec.feed_forward is None) != (spec.feed_forward_norm is None) or spec.norms:
+            raise ValueError("the hyper arrangement takes a mixer with its norm, and a feed-forward with its norm or neither")
+        names = tuple(spec.option("connections", ()))
+        if len(names) != (1 if spec.feed_forward is None else 2):
+            raise ValueError("the hyper arrangement needs the name of one connection for each sublayer")
+        self.streams = int(spec.option("streams", 0))
+        if self.streams < 1:
+            raise ValueError("the hyper arrangement needs the number of streams")
+        for n in (spec.mixer_norm, spec.feed_forward_norm):
+            if n is not None and n.kind != "rmsnorm":
+                raise ValueError("the hyper arrangement folds an RMS norm into the kernel that reads the streams")
+        self.spec, self.names = spec, names
+        self.mixer_norm = NORMS.build(spec.mixer_norm)
+        self.mixer = MIXERS.build(spec.mixer)
+        self.feed_forward_norm = None if spec.feed_forward_norm is None else NORMS.build(spec.feed_forward_norm)
+        self.feed_forward = None if spec.feed_forward is None else FEED_FORWARDS.build(spec.feed_forward)
+        self.connections: List[tuple] = []          # per sublayer: (in, out, mix)
+
+    def parts(self):
+        return (self.mixer_norm, self.mixer) + (() if self.feed_forward is None else (self.feed_forward_norm, self.feed_forward))
+
+    def weight_specs(self, prefix: str = "") -> List[WeightSpec]:
+        out: List[WeightSpec] = []
+        for part in self.parts():
+            out += part.weight_specs(self.spec.prefix)
+        S = self.streams
+        for n in self.names:
+            p = self.spec.prefix + n
+            out += [WeightSpec(p + ".in", (S,), "vector", ("normal_around", 0.2, 1.0 / S)),
+                    WeightSpec(p + ".out", (S,), "vector", ("one_plus_normal", 0.2)),
+                    WeightSpec(p + ".mix", (S, S), "vector", ("normal_around", 0.2, 1.0 / S))]
+        return out
+
+    def bind(self, get) -> None:
+        for part in self.parts():
+            part.bind(lambda name: get(self.spec.prefix + name))
+        self.connections = [tuple(get(self.spec.prefix + n + s).contiguous() for s in (".in", ".out", ".mix")) for n in self.names]
+
+    def _read(self, x, ctx, which: int, norm):
+        from .. import kernels as K
+        h = ctx.empty((x.shape[0], self.spec.mixer.hidden_size))
+        K.hyper(x, self.streams, ctx.stream, in_w=self.connections[which][0], norm_w=norm.weight, eps=norm.spec.eps, h=h)
+        return h
+
+    def _join(self, y, which: int, x, ctx, following):
+        """Sublayer ``which`` has left its result in y: write it into the streams, and read for what follows.  ``following``:
+        (in, norm) of the next sublayer, or "sum" after the last block of the model, or None."""
+        from .. import kernels as K
+        _, out_w, mix = self.connections[which]
+        W = self.spec.mixer.hidden_size
+        if following == "sum":
+            ones = ctx.scratch.get("stream_ones")
+            if ones is None or ones.numel() != self.streams:
+                ones = ctx.scratch["stream_ones"] = torch.ones(self.streams, dtype=torch.float32, device=ctx.device)
+            total = ctx.empty((x.shape[0], W), torch.float32)
+            K.hyper(x, self.streams, ctx.stream, y=y, mix=mix, out_w=out_w, in_w=ones, h=total)
+            ctx.carried["stream_sum"] = (total, ctx.run + 1)
+            return None
+        if following is None:
+            K.hyper(x, self.streams, ctx.stream, y=y, mix=mix, out_w=out_w)
+            return None
+        in_w, norm = following
+        h = ctx.empty((x.shape[0], W))
+        K.hyper(x, self.streams, ctx.stream, y=y, mix=mix, out_w=out_w, in_w=in_w, norm_w=norm.weight, eps=norm.spec.eps, h=h)
+        return h
+
+    def forward(self, x: torch.Tensor, ctx, cache) -> None:
+        W = self.spec.mixer.hidden_size
+        if x.shape[1] != self.streams * W:
+            raise ValueError(f"the hyper arrangement of {self.streams} streams was given rows of {x.shape[1]} elements, not {self.streams * W}")
+        y = ctx.carried.get("sublayer_sum")
+        if y is None or y.shape != (x.shape[0], W):
+            y = ctx.carried["sublayer_sum"] = torch.zeros((x.shape[0], W), dtype=torch.float32, device=ctx.device)   # zeroed once a step; the joining kernel leaves it zeroed
+        kept = ctx.carried.pop("normed_rows", None)
+        h = kept[0] if kept is not None and kept[1] == ctx.run and kept[0].shape == (x.shape[0], W) else self._read(x, ctx, 0, self.mixer_norm)
+        self.mixer.forward(h, ctx, cache, y)
+        nxt = ctx.next_block
+        if nxt is None:
+            following = "sum"
+        elif isinstance(nxt, HyperConnectionBlock) and nxt.streams == self.streams and ctx.options.get("fuse_hyper", True):
+            following = (nxt.connections[0][0], nxt.mixer_norm)
+        else:
+            following = None
+        if self.feed_forward is None:
+            h = self._join(y, 0, x, ctx, following)
+        else:
+            h = self._join(y, 0, x, ctx, (self.connections[1][0], self.feed_forward_norm))
+            self.feed_forward.forward(h, ctx, y)
+            h = self._join(y, 1, x, ctx, following)
+        if h is not None:
+            ctx.carried["normed_rows"] = (h, ctx.run + 1)
+
+
+BLOCKS.register("hyper", HyperConnectionBlock)

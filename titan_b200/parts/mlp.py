@@ -73,3 +73,45 @@ class GatedMLP(FeedForward):
 
 
 FEED_FORWARDS.register("gated_mlp", GatedMLP)
+
+
+class ActivatedMLP(FeedForward):
+    """``mlp``: a feed-forward without a gate, down(act(up(x))), added into the residual stream.  The activation
+    (``FeedForwardSpec.activation``) is ``polynorm``: with z the up-projection's row of ``intermediate_size`` elements and
+    four learned numbers (a, b, c, e) in one tensor (role "act"),
+
+        act(z) = a N(z) + b N(z^2) + c N(z^3) + e,    N(x) = x / sqrt(mean(x^2) + eps)
+
+    powers element by element, the means over the row; ``eps`` is the option "act_eps".  The three means and the result are
+    float32 inside one kernel that reads the row twice; tensor names by role: "up", "down", "act"."""
+
+    def __init__(self, spec):
+        if spec.activation != "polynorm":
+            raise ValueError(f"activation '{spec.activation}' is not supported by the ungated feed-forward ('polynorm')")
+        if spec.intermediate_size <= 0:
+            raise ValueError("intermediate_size must be positive")
+        self.spec = spec
+        self.eps = float(spec.option("act_eps", 1e-6))
+        self.w_up = self.w_down = self.coef = None
+
+    def _names(self):
+        return {role: self.spec.name(role, role) for role in ("up", "down", "act")}
+
+    def weight_specs(self, prefix: str) -> List[WeightSpec]:
+        s, p, n = self.spec, prefix + self.spec.prefix, self._names()
+        return [WeightSpec(p + n["up"], (s.intermediate_size, s.hidden_size)), WeightSpec(p + n["down"], (s.hidden_size, s.intermediate_size)),
+                WeightSpec(p + n["act"], (4,), "vector", ("normal_around", 0.3, 0.5))]
+
+    def bind(self, get) -> None:
+        p, n = self.spec.prefix, self._names()
+        self.w_up, self.w_down, self.coef = get(p + n["up"]), get(p + n["down"]), get(p + n["act"]).contiguous()
+
+    def forward(self, h, ctx, out: torch.Tensor) -> None:
+        h = rows_of(h)
+        z = ctx.empty((h.shape[0], self.spec.intermediate_size))
+        linear.matmul(h, self.w_up, z, linear.EPI_STORE, ctx)
+        K.polynorm(z, self.coef, self.eps, z, ctx.stream)              # in place: a block reads its row before it writes it
+        linear.matmul(z, self.w_down, out, linear.EPI_ADD, ctx)
+
+
+FEED_FORWARDS.register("mlp", ActivatedMLP)

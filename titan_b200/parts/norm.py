@@ -52,9 +52,10 @@ class RMSNorm(Norm):
     def deferred(self, x: torch.Tensor, ctx) -> DeferredNorm:
         return DeferredNorm(self, x, ctx)
 
-    def forward(self, x: torch.Tensor, ctx, rows: Optional[torch.Tensor] = None) -> torch.Tensor:
+    def forward(self, x: torch.Tensor, ctx, rows: Optional[torch.Tensor] = None, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+        """``out_dtype``: the dtype of the normed rows where it is not the compute dtype (float32 for a norm inside the residual stream)."""
         n = x.shape[0] if rows is None else rows.numel()
-        y = ctx.empty((n, self.spec.size))
+        y = ctx.empty((n, self.spec.size), out_dtype)
         K.rmsnorm(x, self.weight, y, self.spec.eps, ctx.stream, rows)
         return y
 

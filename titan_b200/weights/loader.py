@@ -50,7 +50,7 @@ class WeightSpec:
     name: str                         # full tensor name in the file
     shape: Tuple[int, ...]
     role: str = "matrix"              # "matrix" | "vector" | "int_table"
-    init: Tuple[str, float] = ("normal", 0.02)   # ("normal", std) | ("one_plus_normal", std)
+    init: Tuple = ("normal", 0.02)   # ("normal", std) | ("one_plus_normal", std) | ("normal_around", std, mean)
 
 
 def check_names(declared: Iterable[WeightSpec], found: Dict[str, Tuple[Tuple[int, ...], torch.dtype]],

@@ -91,7 +91,9 @@ def values(key: int, start: int, count: int, std: float, mean: float) -> np.ndar
 
 
 def _parameters(spec: WeightSpec):
-    kind, std = spec.init
+    kind, std = spec.init[0], spec.init[1]
+    if kind == "normal_around":                # ("normal_around", std, mean)
+        return float(std), float(spec.init[2])
     if kind not in ("normal", "one_plus_normal"):
         raise ValueError(f"unknown init '{kind}' for {spec.name}")
     return float(std), (1.0 if kind == "one_plus_normal" else 0.0)
