@@ -45,8 +45,8 @@ def rotate_adjacent(x, positions, dims, base):
 
 
 def sees(i, j, size, keep_first):
-    """Does position i see position j: the causal window of ``size`` keys and the first ``keep_first`` tokens."""
-    return j <= i and (i - j < size or j < keep_first)
+    """Does position i see position j: the causal window of ``size`` keys (None: all) and the first ``keep_first`` tokens."""
+    return j <= i and (size is None or i - j < size or j < keep_first)
 
 
 def windowed_sink_attention(h, w, m, eps):
@@ -57,6 +57,7 @@ def windowed_sink_attention(h, w, m, eps):
     k = (h @ w["k"].T).reshape(T, G, dk)
     v = (h @ w["v"].T).reshape(T, G, dv)
     pos = np.arange(T, dtype=np.float64)
+    mask = m.get("mask") or {}
     q = rotate_adjacent(q, pos, m["rot"]["dims"], m["rot"]["base"])
     k = rotate_adjacent(k, pos, m["rot"]["dims"], m["rot"]["base"])
     v = rms_div(v, eps)
@@ -64,7 +65,7 @@ def windowed_sink_attention(h, w, m, eps):
     for hh in range(H):
         g = hh // (H // G)
         for i in range(T):
-            js = [j for j in range(i + 1) if sees(i, j, m["mask"]["size"], m["mask"]["keep_first"])]
+            js = [j for j in range(i + 1) if sees(i, j, mask.get("size"), mask.get("keep_first", 0))]
             s = np.array([q[i, hh] @ k[j, g] for j in js]) * m["scale"]
             top = max(s.max(), w["sink"][hh])
             e = np.exp(s - top)
