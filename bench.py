@@ -586,15 +586,34 @@ def tefezen_config(width, layers, heads, experts, top, ff, shared_ff, window, vo
             "token_side": {"dim": side}, "layers": out}
 
 
-def zadinex_config(width, layers, heads, experts, top, ff, shared_ff, window=None, vocab=32768):
+def vuvosun_config(width, layers, heads, experts, top, ff, shared_ff, window, vocab=32768, streams=4):
+    """A Vuvosun model of the same sizes: layers alternate the parallel mixer (windowed attention with kept first tokens, a
+    sink and an output gate, heads of 128 and a quarter as many kv heads, half of a head rotated; beside it the gated delta
+    rule with heads of 128 and a convolution of four taps) and the mLSTM memory (heads of 128); every layer has the dense
+    polynorm feed-forward, as wide as what a token uses of a mixture; four residual streams."""
+    ffn = {"kind": "dense", "ff": top * ff + shared_ff}
+    out = []
+    for i in range(layers):
+        if i % 2 == 0:
+            out.append({"type": "parallel", "mlp": ffn,
+                        "mixer": {"left": {"heads": heads, "kv_heads": max(1, heads // 4), "dim": 128, "vdim": 128, "rot": {"base": 10000.0, "dims": 64},
+                                           "scale": 128 ** -0.5, "mask": {"size": window, "keep_first": 4}},
+                                  "right": {"heads": heads, "kv_heads": max(1, heads // 4), "dim": 128, "vdim": 128, "conv": 4},
+                                  "left_scale": 1.0, "right_scale": 1.0}})
+        else:
+            out.append({"type": "mlstm", "mixer": {"heads": heads, "dim": 128, "vdim": 128, "gate_cap": 15.0}, "mlp": ffn})
+    return {"architecture": "Vuvosun", "vocab": vocab, "width": width, "streams": streams, "norm": {"eps": 1e-6}, "layers": out}
+
+
+def zadinex_config(width, layers, heads, experts, top, ff, shared_ff, window=None, vocab=32768, dense=False):
     """A Zadinex model of the same sizes: layers alternate attention (heads of 128, a quarter as many kv heads, half of a
     head rotated, values blended from the second attention layer on) and the wkv recurrence (heads of 64); the first layer
     has the dense feed-forward (as wide as what a token uses of a mixture), the others mixtures with four pass-through
-    experts, in four groups of which two are open."""
+    experts, in four groups of which two are open (``dense``: every layer with the dense feed-forward)."""
     moe = {"kind": "moe", "expert": {"ff": ff, "limit": 7.0}, "router": {"experts": experts, "top": top, "identity": 4, "groups": {"count": 4, "keep": 2}}}
     out = []
     for i in range(layers):
-        mlp = {"kind": "dense", "ff": top * ff + shared_ff} if i == 0 else moe
+        mlp = {"kind": "dense", "ff": top * ff + shared_ff} if i == 0 or dense else moe
         if i % 2 == 0:
             out.append({"type": "attention", "mlp": mlp,
                         "mixer": {"heads": heads, "kv_heads": max(1, heads // 4), "dim": 128, "vdim": 128, "rot": {"base": 10000.0, "dims": 64},
@@ -619,7 +638,8 @@ def launcher_times(engine, torch, K, entries):
                          "gemm_tc", "gemm_tc_expert_runs", "gemm_tc_normed", "qk_norm_rope", "kv_append", "attn_prefill", "attn_decode", "attn_decode_mma",
                          "attn_prefill_mma", "attn_prefill_tc", "attn_prefill_split", "moe_gather", "latent_prep", "latent_append", "lightning_scan", "lightning_chunks",
                          "gated_rmsnorm", "moe_route", "token_gate_rows", "moe_plan", "moe_grouped", "moe_rows", "moe_combine", "moe_experts_tc",
-                         "dyt", "scale_add", "wkv", "moe_route_all") if hasattr(K, n)]
+                         "dyt", "scale_add", "wkv", "moe_route_all", "hyper", "polynorm", "gate_rows", "head_norm_gate", "delta_prep",
+                         "recurrent_scan") if hasattr(K, n)]
     events, originals = [], {n: getattr(K, n) for n in names}
 
     def wrap(name, f):
@@ -628,7 +648,10 @@ def launcher_times(engine, torch, K, entries):
             a0.record()
             r = f(*a, **k)
             a1.record()
-            events.append((name + "_" + ("shift", "decay", "scan", "out")[a[1]] if name == "wkv" else name, a0, a1))
+            label = name + "_" + ("shift", "decay", "scan", "out")[a[1]] if name == "wkv" else name
+            if name == "recurrent_scan":
+                label += "_" + ("delta", "mlstm")[a[1]]
+            events.append((label, a0, a1))
             return r
         return g
     for n, f in originals.items():
@@ -647,9 +670,10 @@ def launcher_times(engine, torch, K, entries):
 
 
 def run_design(args):
-    """``--design tefezen | zadinex``: prompt and decode throughput of that design at sizes that resemble a served model's
-    layers (random weights), beside the Qwen3 dense model of equal size (and, for zadinex, beside Tefezen, the closest
-    design: windowed attention, a recurrence, mixtures of experts), and where a step's time goes by launcher."""
+    """``--design tefezen | zadinex | vuvosun``: prompt and decode throughput of that design at sizes that resemble a served
+    model's layers (random weights), beside the Qwen3 dense model of equal size and beside the closest design (for zadinex:
+    Tefezen, windowed attention, a recurrence, mixtures of experts; for vuvosun: Zadinex with dense feed-forwards, attention
+    with a sink and a recurrence over a matrix state), and where a step's time goes by launcher."""
     import torch
 
     from titan_b200 import Engine, StepEntry, kernels as K
@@ -663,8 +687,13 @@ def run_design(args):
     results = []
     for sz in sizes:
         row = {"size": sz}
-        for which in ((args.design, "qwen3") if args.design == "tefezen" else (args.design, "tefezen", "qwen3")):
-            if which == "zadinex":
+        beside = {"tefezen": ("qwen3",), "zadinex": ("tefezen", "qwen3"), "vuvosun": ("zadinex_dense", "qwen3")}[args.design]
+        for which in (args.design,) + beside:
+            if which == "vuvosun":
+                cfg = vuvosun_config(**sz)
+            elif which == "zadinex_dense":
+                cfg = zadinex_config(**sz, dense=True)
+            elif which == "zadinex":
                 cfg = zadinex_config(**sz)
             elif which == "tefezen":
                 cfg = tefezen_config(**sz)
@@ -715,7 +744,7 @@ def main():
     ap.add_argument("--micro", action="store_true", help="time the layer's kernels alone (CUDA events) and exit; text lines, not the JSON line")
     ap.add_argument("--timeline", type=int, default=0, metavar="BATCH", help="when the CTAs of one captured decode step's kernels start, wait and end "
                     "(needs TITAN_B200_NVCC_FLAGS=-DTB_TIMELINE); text lines, not the JSON line")
-    ap.add_argument("--design", default=None, choices=["tefezen", "zadinex"], help="prompt and decode throughput of another design at a few sizes beside "
+    ap.add_argument("--design", default=None, choices=["tefezen", "zadinex", "vuvosun"], help="prompt and decode throughput of another design at a few sizes beside "
                     "the dense model of equal size; one JSON line of its own, the default workload is not run")
     ap.add_argument("--design-size", type=int, default=None, choices=[0, 1], help="with --design: one of its sizes only")
     args = ap.parse_args()

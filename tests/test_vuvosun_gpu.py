@@ -221,6 +221,7 @@ def test_one_key_decides_at_the_edges_of_the_window_and_of_the_kept_tokens(dtype
     m = attention_description(H, G, dim, dim, 2, 1e6, scale, SIZE, KEEP)
     n = LAST + 1
     x = inputs([n], 8)[0]
+    x[far] = x[far] * 1.5                                       # a loud key: its score with its own query grows with the square
     x[-1] = -x[far]
     assert P.sees(LAST, far, SIZE, KEEP) == seen
     W = plain_weights(w, "a.")
@@ -275,28 +276,34 @@ def test_delta_rule_alone(dtype, H, G, dk, dv, taps):
 
 
 def test_delta_rule_remembers_a_value_far_back():
-    """A decay of nearly one and a key that no later key resembles: 300 tokens on, the query that equals that key still
-    reads its value out of the state (float32; whole, and decoded token by token after the write)."""
+    """A decay of nearly one and a key that no later key resembles: 300 tokens on, a query that equals that key reads its
+    value out of the state.  Keys and queries read one half of the input row and values the other, and the last token has
+    the early token's key half but a value half of its own: what it returns is a blend of its own value and the early
+    one, so a state that lost the early write gives another direction (float32; whole, and decoded token by token after the
+    write)."""
     from titan_b200.cache import SequenceCache
     from titan_b200.parts import MIXERS
     H, dk, dv = 1, 16, 16
+    half = WIDTH // 2
     mixer = MIXERS.build(delta_spec(H, H, dk, dv, 1))
     w = weights_for(mixer, 21)
     w["r.A_log"], w["r.dt_bias"] = torch.tensor([-12.0]), torch.tensor([-6.0])      # g = exp(-e^-12 softplus(.)): no forgetting to speak of
     w["r.a"], w["r.b"] = w["r.a"] * 0.0, w["r.b"] * 0.0                                # beta = 1/2 everywhere
+    w["r.q"][:, half:] = 0.0
     w["r.k"] = w["r.q"].clone()
+    w["r.v"][:, :half] = 0.0
     w["r.q.conv"], w["r.k.conv"], w["r.v.conv"] = torch.ones(dk, 1), torch.ones(dk, 1), torch.ones(dv, 1)
     bind(mixer, w, torch.float32)
     n = 300
     x = inputs([n], 22)[0] * 0.05
     x[3] = inputs([1], 23)[0][0] * 4                                # a loud token early on
-    x[-1] = x[3]                                                    # and its like at the end
+    x[-1, :half] = x[3, :half]                                      # and its key, with another value, at the end
     m = right(H, H, dk, dv, 1)
     W = plain_weights(w, "r.")
     want = t64(P.gated_delta(x.numpy(), W, m, 1e-5))
     quiet = x.clone()
     quiet[3] = quiet[4]
-    assert rel_l2(t64(P.gated_delta(quiet.numpy(), W, m, 1e-5))[-1], want[-1]) > 0.05, "the early token does not reach the last position"
+    assert rel_l2(t64(P.gated_delta(quiet.numpy(), W, m, 1e-5))[-1], want[-1]) > 0.3, "the early token does not reach the last position"
     cache = SequenceCache([mixer.cache_need()], 1024, 2, 512, torch.float32, "cuda", mark_freed=True)
     for sizes in ([[n]], [[5]], [[64], [64], [2]]):
         got = drive(mixer_step(mixer, cache), cache, [x], "float32", sizes)[0]
@@ -418,21 +425,28 @@ def run_in_pieces(e, tokens, pieces):
 
 @pytest.mark.parametrize("name,dtype", MODELS)
 def test_whole_prompts_alone(name, dtype):
+    """In float32 every request is held to the bound by itself.  In bfloat16 the requests' rows are judged together, and each
+    row by the row bound: a prompt of two or three tokens has no later tokens over which the rounding of a 40-wide head's
+    q . k sums (about 1e-2 each in 8 bits of mantissa) would average out."""
     wd = world(name)
     e = wd.engine(dtype)
-    for toks in wd.requests:
-        close(run_in_pieces(e, toks, [len(toks)]), wd.plain(toks), dtype, f"{name}: prompt of {len(toks)}")
+    got = [run_in_pieces(e, toks, [len(toks)]) for toks in wd.requests]
+    want = [wd.plain(toks) for toks in wd.requests]
+    if dtype == "float32":
+        for toks, g, w in zip(wd.requests, got, want):
+            close(g, w, dtype, f"{name}: prompt of {len(toks)}")
+    close(torch.cat(got), torch.cat(want), dtype, f"{name}: all prompts")
     e.check_kernels()
     e.cache.check()
 
 
 @pytest.mark.parametrize("name,dtype", MODELS)
 def test_the_sum_of_the_streams_after_every_layer(name, dtype):
-    """Layer by layer: the first layer that differs is named."""
+    """Layer by layer on the longest request: the first layer that differs is named."""
     from titan_b200 import StepEntry
     wd = world(name)
     e = wd.engine(dtype)
-    toks = wd.requests[2]
+    toks = max(wd.requests, key=len)
     seen = []
     e.layer_observer = lambda run, x: seen.append(x.clone())
     try:
