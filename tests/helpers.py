@@ -82,13 +82,15 @@ def rel_l2(a, b):
 TOL = {"float32": 5e-5, "bfloat16": 3e-2}
 
 
-def rows_close(got, want, dtype, what="", row_factor=4.0):
+def rows_close(got, want, dtype, what="", row_factor=4.0, slack=1.0):
     """The whole tensor within the bound, and every row within ``row_factor`` times the bound: one wrong row
-    among a thousand right ones does not hide in the tensor's norm."""
+    among a thousand right ones does not hide in the tensor's norm.  ``slack`` multiplies the bound (for models so narrow
+    that rounding has nothing to average over)."""
     got, want = got.float().cpu(), want.float().cpu()
     assert got.shape == want.shape, f"{what}: shape {tuple(got.shape)} instead of {tuple(want.shape)}"
     err = rel_l2(got, want)
-    assert err < TOL[dtype], f"{what}: relative error {err:.3e} over the bound {TOL[dtype]:.0e}"
+    assert err < slack * TOL[dtype], f"{what}: relative error {err:.3e} over the bound {slack * TOL[dtype]:.0e}"
+    row_factor *= slack
     g, w = got.double().reshape(-1, got.shape[-1]), want.double().reshape(-1, want.shape[-1])
     per_row = (g - w).norm(dim=1) / w.norm(dim=1).clamp_min(1e-30)
     worst = int(per_row.argmax())

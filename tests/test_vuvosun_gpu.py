@@ -171,6 +171,8 @@ ATTENTION_SIZES = [
     (4, 2, 64, 64, 48, 3e4, None, 0),         # no mask at all; bfloat16: the mma.sync kernels
     (4, 2, 64, 64, 64, 1e4, 64, 0),           # a ring of exactly a page; bfloat16: the mma.sync kernels where they take a ring
     (2, 1, 128, 128, 64, 1e4, None, 0),       # bfloat16: the tcgen05 prompt kernel
+    (4, 2, 64, 64, 32, 1e4, 20, 3),           # bfloat16: the mma.sync kernels with kept tokens whose tile the window has left behind
+    (2, 1, 128, 128, 64, 1e4, 40, 70),        # bfloat16: the tcgen05 prompt kernel with two tiles of kept tokens, then the window's
 ]
 
 
@@ -186,11 +188,11 @@ def test_attention_alone(dtype, H, G, dim, vdim, rot, base, size, keep):
     w["a.sink"] = w["a.sink"] * 5 + 1.0                          # sinks that weigh as much as a key or more
     bind(mixer, w, DT[dtype])
     m = attention_description(H, G, dim, vdim, rot, base, 0.4, size, keep)
-    lens = [150, 71]
+    lens = [330 if keep and dim >= 64 else 150, 71]      # long enough for a block of queries that skips tiles between the kept keys and its window
     xs = inputs(lens, 5)
     want = [0.75 * t64(P.windowed_sink_attention(x.numpy(), plain_weights(w, "a."), m, 1e-5)) for x in xs]
     cache = SequenceCache([mixer.cache_need()], 1024, 4, 512, DT[dtype], "cuda", mark_freed=True)
-    for sizes in ([[150, 71]], [[60, 33], [50, 2], [2, 2], [2, 30]], [[1, 1]]):
+    for sizes in ([lens], [[60, 33], [lens[0] - 100, 2], [2, 2], [2, 30]], [[1, 1]]):
         got = drive(mixer_step(mixer, cache), cache, xs, dtype, sizes)
         for i in range(2):
             rows_close(got[i], want[i], dtype, f"sequence {i}, portions {sizes}", row_factor=6.0)
@@ -200,7 +202,7 @@ SIZE, KEEP, LAST = 72 + 9, 5, 229         # a window and a count of kept tokens 
 
 
 @pytest.mark.parametrize("dtype", BOTH)
-@pytest.mark.parametrize("dim", [32, 64])
+@pytest.mark.parametrize("dim", [32, 64, 128])
 @pytest.mark.parametrize("far,seen", [(0, True), (KEEP - 1, True), (KEEP, False), (63, False), (64, False), (LAST - SIZE, False), (LAST - SIZE + 1, True),
                                       (LAST - SIZE + 2, True), (191, True), (192, True), (LAST - 1, True)])
 def test_one_key_decides_at_the_edges_of_the_window_and_of_the_kept_tokens(dtype, dim, far, seen):
@@ -366,8 +368,8 @@ def test_two_mixers_side_by_side_with_their_factors(dtype):
 # --------------------------------------------------------------------------- #
 # whole models
 # --------------------------------------------------------------------------- #
-def close(got, want, dtype, what=""):
-    return rows_close(got, want, dtype, what, row_factor=6.0)
+def close(got, want, dtype, what="", slack=1.0):
+    return rows_close(got, want, dtype, what, row_factor=6.0, slack=slack)
 
 
 class World:
@@ -478,12 +480,15 @@ def test_prompt_then_token_by_token_and_portions_down_to_two(name, dtype):
 @pytest.mark.parametrize("name,dtype", MODELS)
 def test_a_batch_of_unequal_requests_against_each_alone_and_slots_used_again(name, dtype):
     """All requests as one batch of prompts, decoded together while the shorter ones leave; then the same again in the
-    freed slots and pages (which were overwritten when they were freed), in the other order."""
+    freed slots and pages (which were overwritten when they were freed), in the other order.  In float32 every request is
+    held to the plain result by itself; in bfloat16 the requests' rows are judged together against it (a prompt of three tokens
+    has too few rows for its rounding to average out), and each request against the same request run alone."""
     from titan_b200 import StepEntry
     wd = world(name)
     e = wd.engine(dtype)
     reqs = wd.requests
     tail = 6
+    alone = [run_in_pieces(e, r, [max(1, len(r) - tail)]) for r in reqs]
     for turn in range(2):
         order = list(range(len(reqs))) if turn == 0 else list(reversed(range(len(reqs))))
         heads = {i: max(1, len(reqs[i]) - tail) for i in order}
@@ -507,7 +512,10 @@ def test_a_batch_of_unequal_requests_against_each_alone_and_slots_used_again(nam
                 if at[i] == len(reqs[i]):
                     e.free_slot(slots[i])                      # a shorter request leaves; its slot may be taken in the next turn
         for i in order:
-            close(torch.cat(got[i]), wd.plain(reqs[i]), dtype, f"{name}: request {i} in a batch, turn {turn}")
+            if dtype == "float32":
+                close(torch.cat(got[i]), wd.plain(reqs[i]), dtype, f"{name}: request {i} in a batch, turn {turn}")
+            close(torch.cat(got[i]), alone[i], dtype, f"{name}: request {i} in a batch against itself alone, turn {turn}")
+        close(torch.cat([torch.cat(got[i]) for i in order]), torch.cat([wd.plain(reqs[i]) for i in order]), dtype, f"{name}: all requests of a batch, turn {turn}")
         e.cache.check()
     e.check_kernels()
 
@@ -662,7 +670,11 @@ def drawn_config(seed):
 @pytest.mark.parametrize("dtype", BOTH)
 @pytest.mark.parametrize("seed", range(int(os.environ.get("VUVOSUN_DRAWN", "12"))))
 def test_configurations_drawn_at_random(seed, dtype):
-    """A prompt whole, then a second request as a prompt with single tokens after it, in a batch with a third."""
+    """A prompt whole, then a second request as a prompt with single tokens after it, in a batch with a third.  float32 is
+    the sharp test here (a wrong branch costs tens of percent, summation order 1e-6).  In bfloat16 the bound is doubled: the
+    drawn models have heads of four dimensions and feed-forwards of sixteen values whose cubes pass a norm, and a sum of four
+    rounded products does not average its rounding out as a sum of sixty-four does."""
+    slack = 2.0 if dtype == "bfloat16" else 1.0
     from titan_b200 import Engine, StepEntry
     from titan_b200.config import config_from_dict
     cfg = drawn_config(seed)
@@ -670,7 +682,7 @@ def test_configurations_drawn_at_random(seed, dtype):
     W = as_numpy(w)
     e = Engine.from_tensors(config_from_dict(cfg), w, dtype=dtype, max_tokens=1024, max_slots=4, mark_freed_pages=True)
     a, b, c = (random_tokens(n, cfg["vocab"], 7 * seed + n) for n in (75, 130, 9))
-    close(run_in_pieces(e, a, [len(a)]), t64(P.forward(cfg, W, a)[0]), dtype, f"seed {seed}: whole")
+    close(run_in_pieces(e, a, [len(a)]), t64(P.forward(cfg, W, a)[0]), dtype, f"seed {seed}: whole", slack)
     sb, sc = e.alloc_slot(), e.alloc_slot()
     got_b = [e.step([StepEntry(sb, b[:66], list(range(66))), StepEntry(sc, c[:8], [])])[:66]]
     got_b.append(e.step([StepEntry(sb, [b[66]], [0]), StepEntry(sc, [c[8]], [])])[:1])
@@ -678,6 +690,6 @@ def test_configurations_drawn_at_random(seed, dtype):
     for t in b[67:]:
         got_b.append(e.step([StepEntry(sb, [t], [0])]))
     e.free_slot(sb)
-    close(torch.cat(got_b).float().cpu(), t64(P.forward(cfg, W, b)[0]), dtype, f"seed {seed}: prompt in a batch, then single tokens")
+    close(torch.cat(got_b).float().cpu(), t64(P.forward(cfg, W, b)[0]), dtype, f"seed {seed}: prompt in a batch, then single tokens", slack)
     e.check_kernels()
     e.cache.check()

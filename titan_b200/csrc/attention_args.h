@@ -44,7 +44,7 @@ struct AttnArgs {
     // term exp(sink[h] - max), unscaled, without a key and without a value, once per query however the keys are split.
     const float* sink;
     // With a window: the first keep_first positions of a sequence stay visible to every later query, at their true
-    // positions, beside the window's keys (0: the window alone).  The any-size kernels only.
+    // positions, beside the window's keys (0: the window alone).
     int keep_first;
 };
 

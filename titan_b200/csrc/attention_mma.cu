@@ -58,6 +58,7 @@ struct DecArgs {
     __nv_bfloat16* storage; long long v_half;      // the cache's K half and the distance to its V half, in elements
     int late_trigger;                              // the next kernel may start once this one's pages are read (else: at once)
     const float* sink;                             // [nh] or null: one more term exp(sink) of every head's softmax denominator
+    int keep_first;                                // with a window: the sequence's first keep_first keys stay visible
 };
 
 __device__ __forceinline__ void ldsm_x4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
@@ -156,7 +157,11 @@ attn_decode_mma_kernel(const __grid_constant__ CUtensorMap kv_map, DecArgs a) {
     const int group = a.nh / a.nkv;
     const int wlo = a.window > 0 ? max(0, len - a.window) : 0;       // first visible key of position len - 1
     const int lo = max(wlo, (int)min((long long)len, (long long)split * keys)), hi = (int)min((long long)len, (long long)(split + 1) * keys);
-    const int page0 = lo / PAGE, n_pages = lo < hi ? (hi - 1) / PAGE - page0 + 1 : 0;
+    // The kept first keys that lie in this split and before the window: keys [klo, khi), n_keep pages from page kpage0,
+    // which come before the window's pages (a page that holds keys of both is read twice; the masks do not overlap).
+    const int klo = (int)min((long long)len, (long long)split * keys), khi = a.keep_first > 0 ? min(hi, min(a.keep_first, wlo)) : 0;
+    const int kpage0 = klo / PAGE, n_keep = klo < khi ? (khi - 1) / PAGE - kpage0 + 1 : 0;
+    const int page0 = lo / PAGE - n_keep, n_pages = n_keep + (lo < hi ? (hi - 1) / PAGE - lo / PAGE + 1 : 0);      // page i >= n_keep is page0 + i
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) { mbar_init(full + s, 1); mbar_init(empty + s, DEC_WARPS); }
@@ -194,7 +199,7 @@ attn_decode_mma_kernel(const __grid_constant__ CUtensorMap kv_map, DecArgs a) {
                 }
                 const int s = i % STAGES, round = i / STAGES;
                 if (round > 0) mbar_wait(empty + s, (round - 1) & 1, &g_attn_error, 1);
-                const int pos0 = (page0 + i) * PAGE;
+                const int pos0 = (i < n_keep ? kpage0 + i : page0 + i) * PAGE;
                 const int page = tab[(a.ring_rows ? pos0 % a.ring_rows : pos0) / PAGE];
                 const int row = (page * a.nkv + kh) * PAGE;
                 uint8_t* kd = base + s * 2 * TILE_BYTES;
@@ -344,14 +349,15 @@ attn_decode_mma_kernel(const __grid_constant__ CUtensorMap kv_map, DecArgs a) {
             }
         }
         // mask, scale, running softmax
-        const int pos_base = (page0 + i) * PAGE + warp * 16 + 2 * t;
+        const int pos_base = (i < n_keep ? kpage0 + i : page0 + i) * PAGE + warp * 16 + 2 * t;
+        const int vis_lo = i < n_keep ? klo : lo, vis_hi = i < n_keep ? khi : hi;
         float mx0 = -INFINITY, mx1 = -INFINITY;
 #pragma unroll
         for (int j = 0; j < 2; ++j)
 #pragma unroll
             for (int c = 0; c < 2; ++c) {
                 const int pos = pos_base + j * 8 + c;
-                const bool ok = pos >= lo && pos < hi;
+                const bool ok = pos >= vis_lo && pos < vis_hi;
                 sc[j][c] = ok ? sc[j][c] * a.scale_log2 : -INFINITY;
                 sc[j][c + 2] = ok ? sc[j][c + 2] * a.scale_log2 : -INFINITY;
                 mx0 = fmaxf(mx0, sc[j][c]);
@@ -501,6 +507,7 @@ struct PreArgs {
     int paged; const int* start_pos; const int* slot_of_seq; const int* table; int table_width; int v_row0;
     int tail_col0;                           // HDT > 0: first column (in the tail map's rows) of the key dimensions that all heads share
     const float* sink;                       // [nh] or null: one more term exp(sink) of every head's softmax denominator
+    int keep_first;                          // with a window: a sequence's first keep_first keys stay visible to every later query
 };
 
 // HDK: dimensions of a query and of a key; HDV: of a value and of an output row (the same for grouped-query attention).
@@ -537,7 +544,14 @@ attn_prefill_mma_kernel(const __grid_constant__ CUtensorMap qkv_map, const __gri
     const int p0 = a.paged ? a.start_pos[seq] : 0;                   // position of the sequence's first row
     const int last_key = p0 + min(n - 1, r0 + 63);
     const int first_key = a.window > 0 ? max(0, p0 + r0 - a.window + 1) : 0;
-    const int kt0 = first_key >> 6, n_tiles = (last_key >> 6) - kt0 + 1;
+    // the window's tiles from kt0 on and, where the window has left the kept first keys behind by a tile or more, the
+    // n_keep tiles that hold those, ahead of them: tile i holds keys of tile i (i < n_keep) or i + kskip
+    int kt0 = first_key >> 6, n_keep = 0;
+    if (a.keep_first > 0 && a.window > 0) {
+        const int kept_tiles = (a.keep_first + 63) >> 6;
+        if (kt0 > kept_tiles) n_keep = kept_tiles; else kt0 = 0;
+    }
+    const int n_tiles = n_keep + (last_key >> 6) - kt0 + 1, kskip = kt0 - n_keep;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) { mbar_init(full + s, 1); mbar_init(empty + s, DEC_WARPS); }
@@ -557,7 +571,8 @@ attn_prefill_mma_kernel(const __grid_constant__ CUtensorMap qkv_map, const __gri
                 const int s = i % STAGES, round = i / STAGES;
                 if (round > 0) mbar_wait(empty + s, (round - 1) & 1, &g_attn_error, 3);
                 uint8_t* kd = base + s * STAGE_BYTES;
-                const int krow = a.paged ? (tab[kt0 + i] * a.nkv + kh) * 64 : tok0 + (kt0 + i) * 64;
+                const int kt = i < n_keep ? i : i + kskip;
+                const int krow = a.paged ? (tab[kt] * a.nkv + kh) * 64 : tok0 + kt * 64;
                 const int vrow = a.paged ? a.v_row0 + krow : krow;
                 mbar_expect_tx(full + s, STAGE_BYTES);
 #pragma unroll
@@ -611,15 +626,15 @@ attn_prefill_mma_kernel(const __grid_constant__ CUtensorMap qkv_map, const __gri
                 mma_bf16(sc[2 * jp + 1], qf[ks][0], qf[ks][1], qf[ks][2], qf[ks][3], b2, b3);
             }
         }
-        const int key_base = (kt0 + i) * 64 + 2 * t;
+        const int key_base = (i < n_keep ? i : i + kskip) * 64 + 2 * t;
         float mx0 = -INFINITY, mx1 = -INFINITY;
 #pragma unroll
         for (int j = 0; j < 8; ++j)
 #pragma unroll
             for (int c = 0; c < 2; ++c) {
                 const int key = key_base + j * 8 + c;
-                sc[j][c] = (key <= qp0 && key >= lo0) ? sc[j][c] * a.scale_log2 : -INFINITY;
-                sc[j][c + 2] = (key <= qp1 && key >= lo1) ? sc[j][c + 2] * a.scale_log2 : -INFINITY;
+                sc[j][c] = (key <= qp0 && (key >= lo0 || key < a.keep_first)) ? sc[j][c] * a.scale_log2 : -INFINITY;
+                sc[j][c + 2] = (key <= qp1 && (key >= lo1 || key < a.keep_first)) ? sc[j][c + 2] * a.scale_log2 : -INFINITY;
                 mx0 = fmaxf(mx0, sc[j][c]);
                 mx1 = fmaxf(mx1, sc[j][c + 2]);
             }
@@ -744,7 +759,7 @@ extern "C" void tb_attn_decode_set_cluster(int on) { g_decode_cluster = on ? 1 :
 
 // 0 if the tensor-core decode kernel takes this problem, else 1 with the reason in tb_last_error().
 extern "C" int tb_attn_decode_mma_check(const AttnArgs* a, int dtype) {
-    TB_REQUIRE(a->keep_first == 0 || a->window == 0, "attn_decode_mma: a window that keeps a sequence's first tokens is not built here");
+    TB_REQUIRE(a->keep_first >= 0 && (a->keep_first == 0 || a->window == 0 || !a->fused_qk), "attn_decode_mma: kept first tokens beside a window come with the head norm as a kernel of its own");
     TB_REQUIRE(dtype == TB_BF16, "attn_decode_mma: bfloat16 only");
     TB_REQUIRE(a->hd == 64 || a->hd == 128, "attn_decode_mma: head_dim %d is not 64 or 128", a->hd);
     TB_REQUIRE(!a->v_alias && (a->hd_v == 0 || a->hd_v == a->hd), "tensor-core attention: keys and values of one width, stored apart");
@@ -787,7 +802,7 @@ extern "C" int tb_attn_decode_mma(const AttnArgs* args, cudaStream_t stream) {
     d.early_len = a.early_len; d.early_mode = a.early_len ? a.early_mode : 0;
     TB_REQUIRE(d.early_mode >= 0 && d.early_mode <= 2, "attn_decode_mma: early_mode %d (0, 1 or 2)", d.early_mode);
     d.nh = a.nh; d.nkv = a.nkv; d.window = a.window; d.scale_log2 = a.scale * 1.4426950408889634f;
-    d.chunk = a.chunk; d.n_splits = a.n_splits; d.sink = a.sink;
+    d.chunk = a.chunk; d.n_splits = a.n_splits; d.sink = a.sink; d.keep_first = a.window > 0 ? a.keep_first : 0;
     d.out = (__nv_bfloat16*)a.out; d.out_stride = a.out_stride;
     d.acc = nullptr; d.acc_stride = 0; d.q_w = d.k_w = nullptr; d.qk_eps = 0.f; d.rope = TbRotary{nullptr, 0, 0.f, 1.f};
     d.row_sumsq = nullptr; d.row_parts = 0; d.row_width = 1; d.row_eps = 0.f; d.storage = nullptr; d.v_half = 0;
@@ -835,7 +850,7 @@ static int launch_prefill(const CUtensorMap& map, const CUtensorMap& kv_map, con
 // sequence of the step starts at position 0, so all keys are among the step's own rows) or TB_KV_FROM_CACHE (keys
 // and values from the pages of a cache that keeps every key, the step's own appended already).
 extern "C" int tb_attn_prefill_mma_check(const AttnArgs* a, int dtype, int source) {
-    TB_REQUIRE(a->keep_first == 0 || a->window == 0, "attn_prefill_mma: a window that keeps a sequence's first tokens is not built here");
+    TB_REQUIRE(a->keep_first >= 0, "attn_prefill_mma: a negative count of kept tokens");
     TB_REQUIRE(dtype == TB_BF16, "attn_prefill_mma: bfloat16 only");
     TB_REQUIRE(source == TB_KV_FROM_STEP || source == TB_KV_FROM_CACHE, "attn_prefill_mma: a sequence continues from the cache and its keys are not all there");
     TB_REQUIRE(a->hd == 64 || a->hd == 128, "attn_prefill_mma: head_dim %d is not 64 or 128", a->hd);
@@ -869,6 +884,7 @@ extern "C" int tb_attn_prefill_mma(const AttnArgs* args, int source, cudaStream_
     p.out = (__nv_bfloat16*)a.out; p.out_stride = a.out_stride; p.q_start = a.batch.q_start; p.B = a.batch.B;
     p.nh = a.nh; p.nkv = a.nkv; p.window = a.window; p.scale_log2 = a.scale * 1.4426950408889634f;
     p.k_col0 = a.nh * a.hd; p.v_col0 = (a.nh + a.nkv) * a.hd; p.tail_col0 = 0; p.sink = a.sink;
+    p.keep_first = a.window > 0 ? a.keep_first : 0;
     const int blocks = (a.batch.T + 63) / 64 + a.batch.B;          // upper bound on sum over sequences of ceil(n / 64)
     TB_REQUIRE(blocks <= 65535, "attn_prefill_mma: too many query blocks (%d)", blocks);
     dim3 grid(a.nh, blocks);
@@ -916,7 +932,7 @@ extern "C" int tb_attn_prefill_split(const SplitAttnArgs* args, cudaStream_t str
     p.paged = 0; p.start_pos = nullptr; p.slot_of_seq = nullptr; p.table = nullptr; p.table_width = 0; p.v_row0 = 0;
     p.out = (__nv_bfloat16*)a.out; p.out_stride = a.out_stride; p.q_start = a.batch.q_start; p.B = a.batch.B;
     p.nh = a.nh; p.nkv = a.nh; p.window = a.window; p.scale_log2 = a.scale * 1.4426950408889634f;
-    p.k_col0 = a.k_col0; p.v_col0 = a.v_col0; p.tail_col0 = a.tail_col0; p.sink = nullptr;
+    p.k_col0 = a.k_col0; p.v_col0 = a.v_col0; p.tail_col0 = a.tail_col0; p.sink = nullptr; p.keep_first = 0;
     const int blocks = (a.batch.T + 63) / 64 + a.batch.B;
     TB_REQUIRE(blocks <= 65535, "attn_prefill_split: too many query blocks (%d)", blocks);
     dim3 grid(a.nh, blocks);

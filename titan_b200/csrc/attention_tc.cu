@@ -57,6 +57,7 @@ struct TcAttnArgs {
     __nv_bfloat16* out; int out_stride;
     const int* q_start; int B;
     int nh; int nkv; int window; float scale_log2;
+    int keep_first;          // with a window: a sequence's first keep_first keys stay visible to every later query
     int k_col0; int v_col0;
     // keys and values from the cache (continuation steps): the first position of each sequence's rows, its slot,
     // the block table, and the row of the first V page in the cache's tensor map; paged = 0: from the step's rows
@@ -151,7 +152,15 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
     const int p0 = a.paged ? a.start_pos[seq] : 0;                // position of the sequence's first row
     const int last_key = p0 + min(n - 1, r0 + BQ - 1);
     const int first_key = a.window > 0 ? max(0, p0 + r0 - a.window + 1) : 0;
-    const int kt0 = first_key / BKEY, n_tiles = last_key / BKEY - kt0 + 1;
+    // Key tiles of this block: the window's, from tile kt0 to the last query's; and, where the window has left a
+    // sequence's kept first keys behind by at least a tile, the n_keep tiles that hold those, ahead of the window's.
+    int kt0 = first_key / BKEY, n_keep = 0;
+    if (a.keep_first > 0 && a.window > 0) {
+        const int kept_tiles = (a.keep_first + BKEY - 1) / BKEY;
+        if (kt0 > kept_tiles) n_keep = kept_tiles; else kt0 = 0;
+    }
+    const int n_tiles = n_keep + last_key / BKEY - kt0 + 1;
+    const int kskip = kt0 - n_keep;                               // tile j holds keys of tile j (j < n_keep) or j + kskip
 
     if (threadIdx.x == 0) {
         mbar_init(q_full, 1);
@@ -180,8 +189,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
             int ki = 0, vi = 0;
             for (uint32_t spin = 0; (ki < n_tiles || vi < n_tiles) && spin < (tbtma::WAIT_LIMIT << 4); ++spin) {
                 if (ki < n_tiles && (ki < KV_STAGES || tbtma::mbar_test(s_done + ki % KV_STAGES, (ki / KV_STAGES - 1) & 1))) {
-                    const int s = ki % KV_STAGES;
-                    const int row = a.paged ? (tab[kt0 + ki] * a.nkv + kh) * BKEY : tok0 + (kt0 + ki) * BKEY;
+                    const int s = ki % KV_STAGES, kt = ki < n_keep ? ki : ki + kskip;
+                    const int row = a.paged ? (tab[kt] * a.nkv + kh) * BKEY : tok0 + kt * BKEY;
                     uint8_t* kd = kv_smem + s * 2 * KV_TILE;
                     mbar_expect_tx(k_full + s, KV_TILE);
                     tma_load_2d(kd, &kv_map, k_full + s, kx, row);
@@ -189,8 +198,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
                     ++ki; spin = 0;
                 }
                 if (vi < n_tiles && (vi < KV_STAGES || tbtma::mbar_test(pv_done + vi % KV_STAGES, (vi / KV_STAGES - 1) & 1))) {
-                    const int s = vi % KV_STAGES;
-                    const int row = a.paged ? a.v_row0 + (tab[kt0 + vi] * a.nkv + kh) * BKEY : tok0 + (kt0 + vi) * BKEY;
+                    const int s = vi % KV_STAGES, kt = vi < n_keep ? vi : vi + kskip;
+                    const int row = a.paged ? a.v_row0 + (tab[kt] * a.nkv + kh) * BKEY : tok0 + kt * BKEY;
                     uint8_t* vd = kv_smem + s * 2 * KV_TILE + KV_TILE;
                     mbar_expect_tx(v_full + s, KV_TILE);
                     tma_load_2d(vd, &kv_map, v_full + s, vx, row);
@@ -246,8 +255,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
         float m_run = -1e30f, l_run = 0.f;                       // the maximum P is taken against (may lag), the sum
         int mine = 0;                                            // tiles of this group so far
         for (int j = g; j < n_tiles; j += 2, ++mine) {
-            const int key0 = (kt0 + j) * BKEY;
-            const bool tile_visible = key0 + BKEY - 1 <= qpos && key0 >= lo;       // no mask needed in this tile
+            const int key0 = (j < n_keep ? j : j + kskip) * BKEY;
+            const bool tile_visible = key0 + BKEY - 1 <= qpos && (key0 >= lo || key0 + BKEY <= a.keep_first);       // no mask needed in this tile
             wait(s_done + (j & 3), (j >> 2) & 1, 6);
             tc_fence_after();
             float v[64];
@@ -257,7 +266,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
             float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
             if (!tile_visible) {
 #pragma unroll
-                for (int i = 0; i < 64; ++i) v[i] = (key0 + i <= qpos && key0 + i >= lo) ? v[i] : -INFINITY;
+                for (int i = 0; i < 64; ++i) v[i] = (key0 + i <= qpos && (key0 + i >= lo || key0 + i < a.keep_first)) ? v[i] : -INFINITY;
             }
 #pragma unroll
             for (int i = 0; i < 64; i += 8) {               // four chains of three-input maxima
@@ -365,7 +374,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
 // TB_KV_FROM_CACHE (2): they are read from the cache's pages, where the step's own keys already lie (a cache
 // that keeps every key: no ring).
 extern "C" int tb_attn_prefill_tc_check(const AttnArgs* a, int dtype, int source) {
-    TB_REQUIRE(a->keep_first == 0 || a->window == 0, "attn_prefill_tc: a window that keeps a sequence's first tokens is not built here");
+    TB_REQUIRE(a->keep_first >= 0, "attn_prefill_tc: a negative count of kept tokens");
     TB_REQUIRE(dtype == TB_BF16, "attn_prefill_tc: bfloat16 only");
     TB_REQUIRE(source == TB_KV_FROM_STEP || source == TB_KV_FROM_CACHE, "attn_prefill_tc: a sequence continues from the cache and its keys are not all there");
     TB_REQUIRE(a->hd == HD, "attn_prefill_tc: head_dim %d is not %d", a->hd, HD);
@@ -400,6 +409,7 @@ extern "C" int tb_attn_prefill_tc(const AttnArgs* args, int source, cudaStream_t
     p.v_row0 = a.cache.num_pages * a.nkv * BKEY;
     p.out = (__nv_bfloat16*)a.out; p.out_stride = a.out_stride; p.q_start = a.batch.q_start; p.B = a.batch.B;
     p.nh = a.nh; p.nkv = a.nkv; p.window = a.window; p.scale_log2 = a.scale * 1.4426950408889634f; p.sink = a.sink;
+    p.keep_first = a.window > 0 ? a.keep_first : 0;
     p.k_col0 = a.nh * a.hd; p.v_col0 = (a.nh + a.nkv) * a.hd;
     constexpr size_t smem = 1024 + Q_BYTES + KV_STAGES * 2 * KV_TILE + 256 + 4 * 128 * sizeof(float);
     static_assert(KV_STAGES == 4, "the second kernel's barrier layout and S buffers assume four stages");

@@ -11,9 +11,10 @@
 //                 state, which starts as zeros) with silu; q and k heads made unit vectors, q times dk^(-1/2); beta =
 //                 sigmoid(.) and g = exp(-exp(A_log) softplus(. + dt_bias)) per head.  All float32, results float32.
 // tb_recurrent_scan   either recurrence, tokens of a sequence in order whatever the step brings (a prompt, a piece of it,
-//                 one token): a block owns 32 value columns of one head's state, four neighbouring lanes share a column
-//                 (a quarter of its rows in registers each) and add their parts with two shuffles.  Sixteen tokens are
-//                 staged in shared memory at a time.  For the delta rule the block of the first head and first columns
+//                 one token): a block owns 16 value columns of one head's state, eight neighbouring lanes share a column
+//                 (an eighth of its rows in registers each) and add their parts with three shuffles.  Sixteen tokens are
+//                 staged in shared memory at a time, and the next sixteen are on their way from memory into registers
+//                 while these are computed.  For the delta rule the block of the first head and first columns
 //                 also moves the convolution's window on: the last taps - 1 inputs of the sequence become its state.
 #include "common.cuh"
 
@@ -47,6 +48,8 @@ struct ScanArgs {
 
 namespace {
 
+__device__ __forceinline__ float as_float(float x) { return x; }
+__device__ __forceinline__ float as_float(__nv_bfloat16 x) { return __bfloat162float(x); }
 __device__ __forceinline__ float silu_r(float z) { return z / (1.0f + expf(-z)); }
 __device__ __forceinline__ float softplus_r(float z) { return fmaxf(z, 0.f) + log1pf(expf(-fabsf(z))); }
 __device__ __forceinline__ float logsigmoid_r(float z) { return fminf(z, 0.f) - log1pf(expf(-fabsf(z))); }
@@ -94,19 +97,24 @@ __global__ void __launch_bounds__(256) delta_prep_kernel(DeltaPrepArgs a) {
 #define SCAN_DELTA 0
 #define SCAN_MLSTM 1
 #define SCAN_CH 16
+#define SCAN_LANES 8                                    // lanes that share a state column
+#define SCAN_COLS (128 / SCAN_LANES)                    // value columns of a block
 
-template <typename TIN, int MODE, int R>
+// R: state rows a lane holds (a column's dk rows, rounded up, over the eight lanes).  NI: 128-element runs of a q or k row.
+template <typename TIN, int MODE, int R, int NI>
 __global__ void __launch_bounds__(128) recurrent_scan_kernel(ScanArgs a) {
     pdl_launch_dependents();
     pdl_wait();
     extern __shared__ __align__(16) float sm[];
-    constexpr int DKP = 4 * (R + 4);                    // a q or k row in shared memory: four runs of R, each padded by 4
+    constexpr int L = SCAN_LANES, COLS = SCAN_COLS;
+    constexpr int DKP = L * (R + 4);                    // a q or k row in shared memory: eight runs of R, each padded by 4
+    constexpr int NV = SCAN_CH * COLS / 128;
     float* qs = sm;                                     // [SCAN_CH][DKP]
     float* ks = qs + SCAN_CH * DKP;                     // [SCAN_CH][DKP]
-    float* vs = ks + SCAN_CH * DKP;                     // [SCAN_CH][32]
-    float* g0 = vs + SCAN_CH * 32;                      // [SCAN_CH]
+    float* vs = ks + SCAN_CH * DKP;                     // [SCAN_CH][COLS]
+    float* g0 = vs + SCAN_CH * COLS;                    // [SCAN_CH]
     float* g1 = g0 + SCAN_CH;                           // [SCAN_CH]
-    const int b = blockIdx.x, h = blockIdx.y, tid = threadIdx.x, s = tid & 3, col = tid >> 2, j = blockIdx.z * 32 + col;
+    const int b = blockIdx.x, h = blockIdx.y, tid = threadIdx.x, s = tid & (L - 1), col = tid / L, j = blockIdx.z * COLS + col;
     const int dk = a.dk, dv = a.dv, H = a.H;
     const int t0 = a.q_start[b], t1 = a.q_start[b + 1];
     const bool live = j < dv;
@@ -126,70 +134,127 @@ __global__ void __launch_bounds__(128) recurrent_scan_kernel(ScanArgs a) {
     const int qh = h / a.group;
     const TIN* qb = (const TIN*)a.q + (size_t)qh * dk;
     const TIN* kb = (const TIN*)a.k + (size_t)qh * dk;
-    const TIN* vb = (const TIN*)a.v + (size_t)h * dv + blockIdx.z * 32;
+    const TIN* vb = (const TIN*)a.v + (size_t)h * dv + blockIdx.z * COLS;
     for (int e = tid; e < 2 * SCAN_CH * DKP; e += 128) sm[e] = 0.f;      // the padding is read as factors: zeros
-    for (int c0 = t0; c0 < t1; c0 += SCAN_CH) {
-        const int n = min(SCAN_CH, t1 - c0);
-        __syncthreads();                                // the chunk before has been read
-        for (int e = tid; e < n * dk; e += 128) {
-            const int tok = e / dk, i = e - tok * dk, at = tok * DKP + (i / R) * (R + 4) + (i % R);
-            qs[at] = ldf(qb + (size_t)(c0 + tok) * a.q_stride + i) * a.q_scale;
-            ks[at] = ldf(kb + (size_t)(c0 + tok) * a.k_stride + i);
-        }
-        for (int e = tid; e < n * 32; e += 128) {
-            const int tok = e >> 5, c = e & 31;
-            vs[e] = blockIdx.z * 32 + c < dv ? ldf(vb + (size_t)(c0 + tok) * a.v_stride + c) : 0.f;
+
+    // A chunk's rows wait in registers while the chunk before is computed: element i of token tok's q and k rows
+    // (i = tid, tid + 128), two value columns and, in the first threads, a token's two gate numbers.
+    TIN pq[SCAN_CH * NI], pk[SCAN_CH * NI], pv[NV];
+    float pg0 = 0.f, pg1 = 0.f;
+    auto fetch = [&](int c0, int n) {
+#pragma unroll
+        for (int tok = 0; tok < SCAN_CH; ++tok)
+#pragma unroll
+            for (int r = 0; r < NI; ++r) {
+                const int i = tid + 128 * r;
+                if (tok < n && i < dk) {
+                    pq[tok * NI + r] = qb[(size_t)(c0 + tok) * a.q_stride + i];
+                    pk[tok * NI + r] = kb[(size_t)(c0 + tok) * a.k_stride + i];
+                }
+            }
+#pragma unroll
+        for (int r = 0; r < NV; ++r) {
+            const int e = tid + 128 * r, tok = e / COLS, c = e % COLS;
+            if (tok < n && blockIdx.z * COLS + c < dv) pv[r] = vb[(size_t)(c0 + tok) * a.v_stride + c];
         }
         if (tid < n) {
             const float* g = a.gates + (size_t)(c0 + tid) * a.gates_stride;
+            pg0 = g[h]; pg1 = g[H + h];
+        }
+    };
+    auto stash = [&](int n) {
+#pragma unroll
+        for (int tok = 0; tok < SCAN_CH; ++tok)
+#pragma unroll
+            for (int r = 0; r < NI; ++r) {
+                const int i = tid + 128 * r, at = tok * DKP + (i / R) * (R + 4) + (i % R);
+                if (tok < n && i < dk) {
+                    qs[at] = as_float(pq[tok * NI + r]) * a.q_scale;
+                    ks[at] = as_float(pk[tok * NI + r]);
+                }
+            }
+#pragma unroll
+        for (int r = 0; r < NV; ++r) {
+            const int e = tid + 128 * r, tok = e / COLS, c = e % COLS;
+            if (tok < n) vs[e] = blockIdx.z * COLS + c < dv ? as_float(pv[r]) : 0.f;
+        }
+        if (tid < n) {
             if constexpr (MODE == SCAN_DELTA) {
-                g0[tid] = g[h]; g1[tid] = g[H + h];
+                g0[tid] = pg0; g1[tid] = pg1;
             } else {                                    // logarithms of the input gate and of the forget gate, capped
-                g1[tid] = a.cap * tanhf((g[h] + a.i_bias[h]) / a.cap);
-                g0[tid] = logsigmoid_r(a.cap * tanhf((g[H + h] + a.f_bias[h]) / a.cap));
+                g1[tid] = a.cap * tanhf((pg0 + a.i_bias[h]) / a.cap);
+                g0[tid] = logsigmoid_r(a.cap * tanhf((pg1 + a.f_bias[h]) / a.cap));
             }
         }
+    };
+
+    if (t0 < t1) fetch(t0, min(SCAN_CH, t1 - t0));
+    for (int c0 = t0; c0 < t1; c0 += SCAN_CH) {
+        const int n = min(SCAN_CH, t1 - c0);
+        __syncthreads();                                // the chunk before has been read
+        stash(n);
         __syncthreads();
+        if (c0 + SCAN_CH < t1) fetch(c0 + SCAN_CH, min(SCAN_CH, t1 - c0 - SCAN_CH));
         for (int tt = 0; tt < n; ++tt) {
-            const float* qr = qs + tt * DKP + s * (R + 4);
-            const float* kr = ks + tt * DKP + s * (R + 4);
-            const float vj = vs[tt * 32 + col];
-            float acc = 0.f;
+            const float4* qr = reinterpret_cast<const float4*>(qs + tt * DKP + s * (R + 4));
+            const float4* kr = reinterpret_cast<const float4*>(ks + tt * DKP + s * (R + 4));
+            const float vj = vs[tt * COLS + col];
+            float acc;
+            // sums over a lane's rows run as four chains, so that one product does not wait for the one before
             if constexpr (MODE == SCAN_DELTA) {
                 const float decay = g0[tt], beta = g1[tt];
-                float pred = 0.f;
+                float p0 = 0.f, p1 = 0.f, p2 = 0.f, p3 = 0.f;
 #pragma unroll
-                for (int ii = 0; ii < R; ++ii) {
-                    S[ii] *= decay;
-                    pred = fmaf(S[ii], kr[ii], pred);
+                for (int ii = 0; ii < R; ii += 4) {
+                    const float4 k4 = kr[ii >> 2];
+                    S[ii] *= decay; S[ii + 1] *= decay; S[ii + 2] *= decay; S[ii + 3] *= decay;
+                    p0 = fmaf(S[ii], k4.x, p0); p1 = fmaf(S[ii + 1], k4.y, p1);
+                    p2 = fmaf(S[ii + 2], k4.z, p2); p3 = fmaf(S[ii + 3], k4.w, p3);
                 }
+                float pred = (p0 + p1) + (p2 + p3);
                 pred += __shfl_xor_sync(0xffffffffu, pred, 1);
                 pred += __shfl_xor_sync(0xffffffffu, pred, 2);
+                pred += __shfl_xor_sync(0xffffffffu, pred, 4);
                 const float u = beta * (vj - pred);
+                p0 = p1 = p2 = p3 = 0.f;
 #pragma unroll
-                for (int ii = 0; ii < R; ++ii) {
-                    S[ii] = fmaf(kr[ii], u, S[ii]);
-                    acc = fmaf(S[ii], qr[ii], acc);
+                for (int ii = 0; ii < R; ii += 4) {
+                    const float4 k4 = kr[ii >> 2], q4 = qr[ii >> 2];
+                    S[ii] = fmaf(k4.x, u, S[ii]); S[ii + 1] = fmaf(k4.y, u, S[ii + 1]);
+                    S[ii + 2] = fmaf(k4.z, u, S[ii + 2]); S[ii + 3] = fmaf(k4.w, u, S[ii + 3]);
+                    p0 = fmaf(S[ii], q4.x, p0); p1 = fmaf(S[ii + 1], q4.y, p1);
+                    p2 = fmaf(S[ii + 2], q4.z, p2); p3 = fmaf(S[ii + 3], q4.w, p3);
                 }
+                acc = (p0 + p1) + (p2 + p3);
                 acc += __shfl_xor_sync(0xffffffffu, acc, 1);
                 acc += __shfl_xor_sync(0xffffffffu, acc, 2);
+                acc += __shfl_xor_sync(0xffffffffu, acc, 4);
             } else {
                 const float f = g0[tt], i = g1[tt];
                 const float m_new = fmaxf(f + m, i), keep = expf(f + m - m_new), add = expf(i - m_new);
                 m = m_new;
-                float nq = 0.f;
                 const float av = add * vj;
+                float p0 = 0.f, p1 = 0.f, p2 = 0.f, p3 = 0.f, n0 = 0.f, n1 = 0.f, n2 = 0.f, n3 = 0.f;
 #pragma unroll
-                for (int ii = 0; ii < R; ++ii) {
-                    S[ii] = fmaf(keep, S[ii], kr[ii] * av);
-                    nn[ii] = fmaf(keep, nn[ii], add * kr[ii]);
-                    acc = fmaf(S[ii], qr[ii], acc);
-                    nq = fmaf(nn[ii], qr[ii], nq);
+                for (int ii = 0; ii < R; ii += 4) {
+                    const float4 k4 = kr[ii >> 2], q4 = qr[ii >> 2];
+                    S[ii] = fmaf(keep, S[ii], k4.x * av); S[ii + 1] = fmaf(keep, S[ii + 1], k4.y * av);
+                    S[ii + 2] = fmaf(keep, S[ii + 2], k4.z * av); S[ii + 3] = fmaf(keep, S[ii + 3], k4.w * av);
+                    nn[ii] = fmaf(keep, nn[ii], add * k4.x); nn[ii + 1] = fmaf(keep, nn[ii + 1], add * k4.y);
+                    nn[ii + 2] = fmaf(keep, nn[ii + 2], add * k4.z); nn[ii + 3] = fmaf(keep, nn[ii + 3], add * k4.w);
+                    p0 = fmaf(S[ii], q4.x, p0); p1 = fmaf(S[ii + 1], q4.y, p1);
+                    p2 = fmaf(S[ii + 2], q4.z, p2); p3 = fmaf(S[ii + 3], q4.w, p3);
+                    n0 = fmaf(nn[ii], q4.x, n0); n1 = fmaf(nn[ii + 1], q4.y, n1);
+                    n2 = fmaf(nn[ii + 2], q4.z, n2); n3 = fmaf(nn[ii + 3], q4.w, n3);
                 }
+                acc = (p0 + p1) + (p2 + p3);
+                float nq = (n0 + n1) + (n2 + n3);
                 acc += __shfl_xor_sync(0xffffffffu, acc, 1);
-                acc += __shfl_xor_sync(0xffffffffu, acc, 2);
                 nq += __shfl_xor_sync(0xffffffffu, nq, 1);
+                acc += __shfl_xor_sync(0xffffffffu, acc, 2);
                 nq += __shfl_xor_sync(0xffffffffu, nq, 2);
+                acc += __shfl_xor_sync(0xffffffffu, acc, 4);
+                nq += __shfl_xor_sync(0xffffffffu, nq, 4);
                 acc = acc / (fmaxf(fabsf(nq), expf(-m_new)) + 1e-6f);
             }
             if (s == 0 && live) a.out[(size_t)(c0 + tt) * a.out_stride + (size_t)h * dv + j] = acc;
@@ -214,17 +279,17 @@ __global__ void __launch_bounds__(128) recurrent_scan_kernel(ScanArgs a) {
         // The sequence's last n_taps - 1 inputs become the convolution's state: from the step's rows, or, where the step
         // brought fewer, from the old state moved up.  A thread owns a channel and goes from the oldest row on, so that
         // it reads every old row before it writes over it.
-        const int C = a.conv_channels, rows = a.n_taps - 1, L = t1 - t0;
+        const int C = a.conv_channels, rows = a.n_taps - 1, Ls = t1 - t0;
         float* st = slot_state + a.conv_off;
         for (int c = tid; c < C; c += 128) {
             for (int r = 0; r < rows; ++r) {
-                const int idx = L - rows + r;
+                const int idx = Ls - rows + r;
                 float x;
                 if (idx >= 0) {
                     const size_t at = (size_t)(t0 + idx) * a.conv_stride + c;
                     x = a.conv_bf16 ? __bfloat162float(((const __nv_bfloat16*)a.conv_in)[at]) : ((const float*)a.conv_in)[at];
                 } else {
-                    x = st[(size_t)(r + L) * C + c];
+                    x = st[(size_t)(r + Ls) * C + c];
                 }
                 st[(size_t)r * C + c] = x;
             }
@@ -232,22 +297,23 @@ __global__ void __launch_bounds__(128) recurrent_scan_kernel(ScanArgs a) {
     }
 }
 
-template <typename TIN, int MODE, int R>
+template <typename TIN, int MODE, int R, int NI>
 int launch_scan_r(const ScanArgs& a, cudaStream_t stream) {
-    constexpr size_t smem = (size_t)(2 * SCAN_CH * 4 * (R + 4) + SCAN_CH * 32 + 2 * SCAN_CH) * sizeof(float);
+    constexpr size_t smem = (size_t)(2 * SCAN_CH * SCAN_LANES * (R + 4) + SCAN_CH * SCAN_COLS + 2 * SCAN_CH) * sizeof(float);
     static_assert(smem <= 48 * 1024, "the staging area fits the default shared memory");
-    dim3 grid(a.B, a.H, (a.dv + 31) / 32);
-    tb_launch(recurrent_scan_kernel<TIN, MODE, R>, grid, dim3(128), smem, stream, a);
+    static_assert(128 * NI >= SCAN_LANES * R || NI == 2, "a q row is fetched in runs of 128 elements");
+    dim3 grid(a.B, a.H, (a.dv + SCAN_COLS - 1) / SCAN_COLS);
+    tb_launch(recurrent_scan_kernel<TIN, MODE, R, NI>, grid, dim3(128), smem, stream, a);
     return 0;
 }
 
 template <typename TIN, int MODE>
 int launch_scan(const ScanArgs& a, cudaStream_t stream) {
-    const int rows = (a.dk + 3) / 4;
-    if (rows <= 8) return launch_scan_r<TIN, MODE, 8>(a, stream);
-    if (rows <= 16) return launch_scan_r<TIN, MODE, 16>(a, stream);
-    if (rows <= 32) return launch_scan_r<TIN, MODE, 32>(a, stream);
-    return launch_scan_r<TIN, MODE, 64>(a, stream);
+    const int rows = (a.dk + SCAN_LANES - 1) / SCAN_LANES;
+    if (rows <= 4) return launch_scan_r<TIN, MODE, 4, 1>(a, stream);
+    if (rows <= 8) return launch_scan_r<TIN, MODE, 8, 1>(a, stream);
+    if (rows <= 16) return launch_scan_r<TIN, MODE, 16, 1>(a, stream);
+    return launch_scan_r<TIN, MODE, 32, 2>(a, stream);
 }
 
 }  // namespace

@@ -316,7 +316,7 @@ class AttentionMixer(Mixer):
         aa.sink = None if self.sink is None else self.sink.data_ptr()
         aa.keep_first = self.keep_first if s.window else 0
         if decode:
-            fast = ctx.options.get("attention", "fast") != "plain" and q_buf.dtype == torch.bfloat16 and hd in (64, 128) and not aa.keep_first
+            fast = ctx.options.get("attention", "fast") != "plain" and q_buf.dtype == torch.bfloat16 and hd in (64, 128)
             chunk, splits = decode_split(lay, view.kv_heads, ctx.options, fast)
             need = lay.B * s.num_heads * splits * (hd + 2)
             scratch = ctx.scratch.get("attn_partials")
@@ -353,7 +353,7 @@ class AttentionMixer(Mixer):
                 source = K.KV_FROM_CACHE
             else:
                 source = K.KV_NOWHERE
-            if hd not in (64, 128) or aa.keep_first:      # what the tensor-core kernels are built for: nothing else asks for (and compiles) them
+            if hd not in (64, 128):                       # what the tensor-core kernels are built for: nothing else asks for (and compiles) them
                 source = K.KV_NOWHERE
             if mode == "fast" and source and K.attn_prefill_tc_accepts(aa, q_buf.dtype, source):
                 K.attn_prefill_tc(aa, source, ctx.stream)
