@@ -11,11 +11,11 @@
 //                 state, which starts as zeros) with silu; q and k heads made unit vectors, q times dk^(-1/2); beta =
 //                 sigmoid(.) and g = exp(-exp(A_log) softplus(. + dt_bias)) per head.  All float32, results float32.
 // tb_recurrent_scan   either recurrence, tokens of a sequence in order whatever the step brings (a prompt, a piece of it,
-//                 one token): a block owns 16 value columns of one head's state, eight neighbouring lanes share a column
-//                 (an eighth of its rows in registers each) and add their parts with three shuffles.  Sixteen tokens are
+//                 one token): a block owns 8 value columns of one head's state, sixteen neighbouring lanes share a column
+//                 (a sixteenth of its rows in registers each) and add their parts with four shuffles.  Sixteen tokens are
 //                 staged in shared memory at a time, and the next sixteen are on their way from memory into registers
-//                 while these are computed.  For the delta rule the block of the first head and first columns
-//                 also moves the convolution's window on: the last taps - 1 inputs of the sequence become its state.
+//                 while these are computed.  For the delta rule the sequence's blocks, a share of the channels each,
+//                 also move the convolution's window on: the last taps - 1 inputs of the sequence become its state.
 #include "common.cuh"
 
 struct DeltaPrepArgs {
@@ -97,18 +97,23 @@ __global__ void __launch_bounds__(256) delta_prep_kernel(DeltaPrepArgs a) {
 #define SCAN_DELTA 0
 #define SCAN_MLSTM 1
 #define SCAN_CH 16
-#define SCAN_LANES 8                                    // lanes that share a state column
+#ifndef SCAN_LANES
+#define SCAN_LANES 8
+#endif                                   // lanes that share a state column
+#ifndef SCAN_UNROLL
+#define SCAN_UNROLL 4                                   // tokens of the inner loop laid out together, so that one's loads pass under another's sums
+#endif
 #define SCAN_COLS (128 / SCAN_LANES)                    // value columns of a block
 
-// R: state rows a lane holds (a column's dk rows, rounded up, over the eight lanes).  NI: 128-element runs of a q or k row.
+// R: state rows a lane holds (a column's dk rows, rounded up, over the sixteen lanes).  NI: 128-element runs of a q or k row.
 template <typename TIN, int MODE, int R, int NI>
 __global__ void __launch_bounds__(128) recurrent_scan_kernel(ScanArgs a) {
     pdl_launch_dependents();
     pdl_wait();
     extern __shared__ __align__(16) float sm[];
-    constexpr int L = SCAN_LANES, COLS = SCAN_COLS;
-    constexpr int DKP = L * (R + 4);                    // a q or k row in shared memory: eight runs of R, each padded by 4
-    constexpr int NV = SCAN_CH * COLS / 128;
+    constexpr int L = SCAN_LANES, COLS = SCAN_COLS, TOKENS_UNROLLED = SCAN_UNROLL;
+    constexpr int DKP = L * (R + 4);                    // a q or k row in shared memory: sixteen runs of R, each padded by 4
+    constexpr int NV = (SCAN_CH * COLS + 127) / 128;
     float* qs = sm;                                     // [SCAN_CH][DKP]
     float* ks = qs + SCAN_CH * DKP;                     // [SCAN_CH][DKP]
     float* vs = ks + SCAN_CH * DKP;                     // [SCAN_CH][COLS]
@@ -138,7 +143,7 @@ __global__ void __launch_bounds__(128) recurrent_scan_kernel(ScanArgs a) {
     for (int e = tid; e < 2 * SCAN_CH * DKP; e += 128) sm[e] = 0.f;      // the padding is read as factors: zeros
 
     // A chunk's rows wait in registers while the chunk before is computed: element i of token tok's q and k rows
-    // (i = tid, tid + 128), two value columns and, in the first threads, a token's two gate numbers.
+    // (i = tid, tid + 128), a value column and, in the first threads, a token's two gate numbers.
     TIN pq[SCAN_CH * NI], pk[SCAN_CH * NI], pv[NV];
     float pg0 = 0.f, pg1 = 0.f;
     auto fetch = [&](int c0, int n) {
@@ -195,40 +200,46 @@ __global__ void __launch_bounds__(128) recurrent_scan_kernel(ScanArgs a) {
         stash(n);
         __syncthreads();
         if (c0 + SCAN_CH < t1) fetch(c0 + SCAN_CH, min(SCAN_CH, t1 - c0 - SCAN_CH));
+#pragma unroll TOKENS_UNROLLED
         for (int tt = 0; tt < n; ++tt) {
             const float4* qr = reinterpret_cast<const float4*>(qs + tt * DKP + s * (R + 4));
             const float4* kr = reinterpret_cast<const float4*>(ks + tt * DKP + s * (R + 4));
             const float vj = vs[tt * COLS + col];
             float acc;
-            // sums over a lane's rows run as four chains, so that one product does not wait for the one before
+            // sums over a lane's rows run as four chains each, so that one product does not wait for the one before
             if constexpr (MODE == SCAN_DELTA) {
+                // Both read-outs of the state come from the state BEFORE this token's write, side by side: with
+                // S' = g S + k u^T, the prediction is g (S^T k) and the output S'^T q = g (S^T q) + (k . q) u.  The two
+                // sums and k . q cross the lanes together, and only u stands between a token's sums and the next one's.
                 const float decay = g0[tt], beta = g1[tt];
-                float p0 = 0.f, p1 = 0.f, p2 = 0.f, p3 = 0.f;
-#pragma unroll
-                for (int ii = 0; ii < R; ii += 4) {
-                    const float4 k4 = kr[ii >> 2];
-                    S[ii] *= decay; S[ii + 1] *= decay; S[ii + 2] *= decay; S[ii + 3] *= decay;
-                    p0 = fmaf(S[ii], k4.x, p0); p1 = fmaf(S[ii + 1], k4.y, p1);
-                    p2 = fmaf(S[ii + 2], k4.z, p2); p3 = fmaf(S[ii + 3], k4.w, p3);
-                }
-                float pred = (p0 + p1) + (p2 + p3);
-                pred += __shfl_xor_sync(0xffffffffu, pred, 1);
-                pred += __shfl_xor_sync(0xffffffffu, pred, 2);
-                pred += __shfl_xor_sync(0xffffffffu, pred, 4);
-                const float u = beta * (vj - pred);
-                p0 = p1 = p2 = p3 = 0.f;
+                float p0 = 0.f, p1 = 0.f, p2 = 0.f, p3 = 0.f, r0 = 0.f, r1 = 0.f, r2 = 0.f, r3 = 0.f, c0s = 0.f, c1s = 0.f, c2s = 0.f, c3s = 0.f;
+                float4 kk[R / 4];
 #pragma unroll
                 for (int ii = 0; ii < R; ii += 4) {
                     const float4 k4 = kr[ii >> 2], q4 = qr[ii >> 2];
-                    S[ii] = fmaf(k4.x, u, S[ii]); S[ii + 1] = fmaf(k4.y, u, S[ii + 1]);
-                    S[ii + 2] = fmaf(k4.z, u, S[ii + 2]); S[ii + 3] = fmaf(k4.w, u, S[ii + 3]);
-                    p0 = fmaf(S[ii], q4.x, p0); p1 = fmaf(S[ii + 1], q4.y, p1);
-                    p2 = fmaf(S[ii + 2], q4.z, p2); p3 = fmaf(S[ii + 3], q4.w, p3);
+                    kk[ii >> 2] = k4;
+                    p0 = fmaf(S[ii], k4.x, p0); p1 = fmaf(S[ii + 1], k4.y, p1);
+                    p2 = fmaf(S[ii + 2], k4.z, p2); p3 = fmaf(S[ii + 3], k4.w, p3);
+                    r0 = fmaf(S[ii], q4.x, r0); r1 = fmaf(S[ii + 1], q4.y, r1);
+                    r2 = fmaf(S[ii + 2], q4.z, r2); r3 = fmaf(S[ii + 3], q4.w, r3);
+                    c0s = fmaf(k4.x, q4.x, c0s); c1s = fmaf(k4.y, q4.y, c1s);
+                    c2s = fmaf(k4.z, q4.z, c2s); c3s = fmaf(k4.w, q4.w, c3s);
                 }
-                acc = (p0 + p1) + (p2 + p3);
-                acc += __shfl_xor_sync(0xffffffffu, acc, 1);
-                acc += __shfl_xor_sync(0xffffffffu, acc, 2);
-                acc += __shfl_xor_sync(0xffffffffu, acc, 4);
+                float pred = (p0 + p1) + (p2 + p3), read = (r0 + r1) + (r2 + r3), kq = (c0s + c1s) + (c2s + c3s);
+#pragma unroll
+                for (int d = 1; d < L; d <<= 1) {
+                    pred += __shfl_xor_sync(0xffffffffu, pred, d);
+                    read += __shfl_xor_sync(0xffffffffu, read, d);
+                    kq += __shfl_xor_sync(0xffffffffu, kq, d);
+                }
+                const float u = beta * (vj - decay * pred);
+                acc = fmaf(kq, u, decay * read);
+#pragma unroll
+                for (int ii = 0; ii < R; ii += 4) {
+                    const float4 k4 = kk[ii >> 2];
+                    S[ii] = fmaf(decay, S[ii], k4.x * u); S[ii + 1] = fmaf(decay, S[ii + 1], k4.y * u);
+                    S[ii + 2] = fmaf(decay, S[ii + 2], k4.z * u); S[ii + 3] = fmaf(decay, S[ii + 3], k4.w * u);
+                }
             } else {
                 const float f = g0[tt], i = g1[tt];
                 const float m_new = fmaxf(f + m, i), keep = expf(f + m - m_new), add = expf(i - m_new);
@@ -249,12 +260,11 @@ __global__ void __launch_bounds__(128) recurrent_scan_kernel(ScanArgs a) {
                 }
                 acc = (p0 + p1) + (p2 + p3);
                 float nq = (n0 + n1) + (n2 + n3);
-                acc += __shfl_xor_sync(0xffffffffu, acc, 1);
-                nq += __shfl_xor_sync(0xffffffffu, nq, 1);
-                acc += __shfl_xor_sync(0xffffffffu, acc, 2);
-                nq += __shfl_xor_sync(0xffffffffu, nq, 2);
-                acc += __shfl_xor_sync(0xffffffffu, acc, 4);
-                nq += __shfl_xor_sync(0xffffffffu, nq, 4);
+#pragma unroll
+                for (int d = 1; d < L; d <<= 1) {
+                    acc += __shfl_xor_sync(0xffffffffu, acc, d);
+                    nq += __shfl_xor_sync(0xffffffffu, nq, d);
+                }
                 acc = acc / (fmaxf(fabsf(nq), expf(-m_new)) + 1e-6f);
             }
             if (s == 0 && live) a.out[(size_t)(c0 + tt) * a.out_stride + (size_t)h * dv + j] = acc;
@@ -275,13 +285,14 @@ __global__ void __launch_bounds__(128) recurrent_scan_kernel(ScanArgs a) {
         }
         if (s == 0) *m_g = m;
     }
-    if constexpr (MODE == SCAN_DELTA) if (a.conv_in && h == 0 && blockIdx.z == 0 && a.n_taps > 1) {
+    if constexpr (MODE == SCAN_DELTA) if (a.conv_in && a.n_taps > 1) {
         // The sequence's last n_taps - 1 inputs become the convolution's state: from the step's rows, or, where the step
-        // brought fewer, from the old state moved up.  A thread owns a channel and goes from the oldest row on, so that
-        // it reads every old row before it writes over it.
+        // brought fewer, from the old state moved up.  The sequence's blocks share the channels; a thread owns a channel
+        // and goes from the oldest row on, so that it reads every old row before it writes over it.
         const int C = a.conv_channels, rows = a.n_taps - 1, Ls = t1 - t0;
+        const int block = h * gridDim.z + blockIdx.z, blocks = H * gridDim.z;
         float* st = slot_state + a.conv_off;
-        for (int c = tid; c < C; c += 128) {
+        for (int c = block * 128 + tid; c < C; c += blocks * 128) {
             for (int r = 0; r < rows; ++r) {
                 const int idx = Ls - rows + r;
                 float x;
@@ -301,19 +312,26 @@ template <typename TIN, int MODE, int R, int NI>
 int launch_scan_r(const ScanArgs& a, cudaStream_t stream) {
     constexpr size_t smem = (size_t)(2 * SCAN_CH * SCAN_LANES * (R + 4) + SCAN_CH * SCAN_COLS + 2 * SCAN_CH) * sizeof(float);
     static_assert(smem <= 48 * 1024, "the staging area fits the default shared memory");
-    static_assert(128 * NI >= SCAN_LANES * R || NI == 2, "a q row is fetched in runs of 128 elements");
+    static_assert(128 * NI >= SCAN_LANES * R, "a q row is fetched in runs of 128 elements");
     dim3 grid(a.B, a.H, (a.dv + SCAN_COLS - 1) / SCAN_COLS);
     tb_launch(recurrent_scan_kernel<TIN, MODE, R, NI>, grid, dim3(128), smem, stream, a);
     return 0;
 }
 
+template <typename TIN, int MODE, int R>
+int launch_scan_rows(const ScanArgs& a, cudaStream_t stream) {
+    return launch_scan_r<TIN, MODE, R, (SCAN_LANES * R > 128 ? 2 : 1)>(a, stream);
+}
+
 template <typename TIN, int MODE>
 int launch_scan(const ScanArgs& a, cudaStream_t stream) {
+    constexpr int MOST = 256 / SCAN_LANES;              // rows a lane holds at 256 key dimensions
     const int rows = (a.dk + SCAN_LANES - 1) / SCAN_LANES;
-    if (rows <= 4) return launch_scan_r<TIN, MODE, 4, 1>(a, stream);
-    if (rows <= 8) return launch_scan_r<TIN, MODE, 8, 1>(a, stream);
-    if (rows <= 16) return launch_scan_r<TIN, MODE, 16, 1>(a, stream);
-    return launch_scan_r<TIN, MODE, 32, 2>(a, stream);
+    if (rows <= 4 || MOST <= 4) return launch_scan_rows<TIN, MODE, 4>(a, stream);
+    if (rows <= 8 || MOST <= 8) return launch_scan_rows<TIN, MODE, (MOST < 8 ? MOST : 8)>(a, stream);
+    if (rows <= 16 || MOST <= 16) return launch_scan_rows<TIN, MODE, (MOST < 16 ? MOST : 16)>(a, stream);
+    if (rows <= 32 || MOST <= 32) return launch_scan_rows<TIN, MODE, (MOST < 32 ? MOST : 32)>(a, stream);
+    return launch_scan_rows<TIN, MODE, MOST>(a, stream);
 }
 
 }  // namespace
