@@ -177,7 +177,7 @@ attn_decode_mma_kernel(const __grid_constant__ CUtensorMap kv_map, DecArgs a) {
     }
     __syncthreads();
     // CL: no CTA may send its part before every CTA of the cluster has its barrier; the arrival is here, the wait
-    // where the parts are sent, long after the cluster's barrier has completed
+    // just before the parts are sent, long after the cluster's barrier has completed
     if (CL) tbtma::cluster_arrive();
     probe.attach();
 
@@ -417,6 +417,10 @@ attn_decode_mma_kernel(const __grid_constant__ CUtensorMap kv_map, DecArgs a) {
         mm[warp * 16 + g + 8] = WIDE ? m1 : -1e30f; ml[warp * 16 + g + 8] = WIDE ? l1 : 0.f;
     }
     asm volatile("bar.sync 1, %0;" ::"n"(DEC_WARPS * 32));
+    // CL: nothing is sent to another CTA before every CTA of the cluster has initialised the barrier that counts what it
+    // receives (a CTA without pages gets here within a microsecond of its start; a sibling that starts later than that
+    // would lose the bytes and wait for them until its limit).  The arrivals were long ago, so this wait costs nothing.
+    if (CL) tbtma::cluster_wait();
     const float ln2 = 0.69314718055994531f;
     for (int idx = threadIdx.x; idx < group * HD; idx += DEC_WARPS * 32) {
         const int row = idx / HD, d = idx % HD;
@@ -453,7 +457,7 @@ attn_decode_mma_kernel(const __grid_constant__ CUtensorMap kv_map, DecArgs a) {
         // part to the CTAs that merge it (above), waits until its own barrier has counted the bytes of every split,
         // merges its share from its own shared memory and leaves.  Nobody reads this CTA's memory, and nobody writes
         // to it after the last of the bytes it waits for.
-        tbtma::cluster_wait();                                      // every thread; completed long ago (see the arrival above)
+        if (warp >= DEC_WARPS) tbtma::cluster_wait();               // the producer's half of the split barrier; the compute warps waited before they sent
         if (warp < DEC_WARPS) {
             if (a.n_splits > 1) tbtma::mbar_wait_cluster(merge_bar, 0, &g_attn_error, 8);      // every split's values have landed here
             if (threadIdx.x == 0) probe.stamp(5);
