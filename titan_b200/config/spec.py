@@ -28,6 +28,7 @@ class NormSpec:
     eps: float
     weight: str               # tensor name relative to the owner's prefix
     weight_offset: float = 0.0  # the rows are multiplied by (weight_offset + stored weight): 1.0 for weights stored around zero
+    groups: int = 1           # the row is cut into this many equal runs, each divided by its own root mean square (1: the whole row by one)
 
 
 @dataclass(frozen=True)
@@ -47,7 +48,7 @@ def _lookup(pairs, key, default):
 
 @dataclass(frozen=True)
 class MixerSpec:
-    kind: str                 # "attention" | "latent_attention" | "lightning" | "wkv" | "gated_delta" | "mlstm" | "parallel"
+    kind: str                 # "attention" | "latent_attention" | "lightning" | "retention" | "wkv" | "gated_delta" | "mlstm" | "parallel"
     hidden_size: int
     num_heads: int = 0
     num_kv_heads: int = 0
@@ -97,7 +98,7 @@ class LayerSpec:
     feed-forward (None), or take more norms than two from ``norms`` (a norm after each part as well as
     before it, say) and its own constants from ``extra``."""
     index: int
-    arrangement: str          # "pre_norm" | "pre_norm_scaled" | "output_norm" | "hyper"
+    arrangement: str          # "pre_norm" | "pre_norm_scaled" | "output_norm" | "hyper" | "parallel"
     mixer: MixerSpec
     feed_forward: Optional[FeedForwardSpec]
     mixer_norm: Optional[NormSpec]

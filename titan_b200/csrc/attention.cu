@@ -232,7 +232,8 @@ __global__ void attn_merge_kernel(AttnArgs a) {
         }
     }
     if (sunk) l += expf(a.sink[h] - m);               // the sink counts once, here, not once a split
-    const float inv = 1.0f / l;
+    float inv = 1.0f / l;
+    if (a.head_gate) inv *= 1.0f / (1.0f + expf(-a.head_gate[(size_t)b * a.head_gate_stride + h]));      // the head's gate
     T* o = (T*)a.out + (size_t)b * a.out_stride + h * hd;
 #pragma unroll
     for (int j = 0; j < PER; ++j) {
@@ -248,6 +249,7 @@ static int check_common(const AttnArgs& a, const char* who) {
     TB_REQUIRE(!a.v_alias || value_width(a) <= a.hd, "%s: a value that is the head of its key row cannot be wider (%d) than the key (%d)", who, value_width(a), a.hd);
     TB_REQUIRE(a.q_stride % 8 == 0 && a.kv_stride % 8 == 0, "%s: row strides must be multiples of 8 elements", who);
     TB_REQUIRE(a.window >= 0 && a.keep_first >= 0, "%s: negative window or kept tokens", who);
+    TB_REQUIRE(!(a.softcap > 0.f) && !a.rel_bias && !a.head_mix, "%s: capped, biased or mixed scores run on the mixed-heads kernels", who);
     TB_REQUIRE(!a.cache.storage || (a.cache.head_dim == a.hd && a.cache.kv_heads == a.nkv), "%s: the cache view does not match the heads", who);
     return 0;
 }
@@ -272,6 +274,7 @@ extern "C" int tb_attn_prefill(const AttnArgs* args, int dtype, cudaStream_t str
     TB_REQUIRE(dtype == TB_F32 || dtype == TB_BF16, "attn_prefill: unknown dtype %d", dtype);
     TB_REQUIRE(a.batch.T > 0, "attn_prefill: no tokens");
     TB_REQUIRE(a.kv_new || a.cache.storage, "attn_prefill: neither new keys nor a cache");
+    TB_REQUIRE(!a.head_gate, "attn_prefill: a gate on the heads is applied by the merge of decode splits or by the mixed-heads kernels");
     dim3 grid(a.batch.T, (a.nh + ATT_WARPS - 1) / ATT_WARPS);
     const size_t smem = (size_t)ATT_WARPS * a.hd * sizeof(float);
     const bool wide = wide_rows(a);

@@ -46,6 +46,15 @@ struct AttnArgs {
     // With a window: the first keep_first positions of a sequence stay visible to every later query, at their true
     // positions, beside the window's keys (0: the window alone).
     int keep_first;
+    // Scores shaped before the softmax (the mixed-heads kernels, attention_mixed.cu; all zero / null: none of it).
+    // softcap > 0: s <- softcap * tanh(s / softcap) after the scale.  rel_bias: a table [rel_far + 1][nh] (float32) of
+    // which row min(query position - key position, rel_far) is added to the capped scores of the nh heads.  head_mix:
+    // [nh][nh] (float32); the score of head h becomes sum_g head_mix[h][g] * score_g, all heads of one (query, key) pair
+    // together, before the softmax.
+    float softcap; const float* rel_bias; int rel_far; const float* head_mix;
+    // One gate a (token, head): head_gate[t * head_gate_stride + h] (float32 logits; null: none) multiplies head h's
+    // output row by its sigmoid where the softmax is finished (the any-size merge and the mixed-heads kernels).
+    const float* head_gate; int head_gate_stride;
 };
 
 // How decode attention cuts the keys of ONE sequence into splits: ``chunk`` keys each while ``n_splits`` of

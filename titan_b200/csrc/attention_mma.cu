@@ -763,6 +763,7 @@ extern "C" void tb_attn_decode_set_cluster(int on) { g_decode_cluster = on ? 1 :
 
 // 0 if the tensor-core decode kernel takes this problem, else 1 with the reason in tb_last_error().
 extern "C" int tb_attn_decode_mma_check(const AttnArgs* a, int dtype) {
+    TB_REQUIRE(!(a->softcap > 0.f) && !a->rel_bias && !a->head_mix && !a->head_gate, "attn_decode_mma: capped, biased, mixed or gated scores run on the mixed-heads kernels");
     TB_REQUIRE(a->keep_first >= 0 && (a->keep_first == 0 || a->window == 0 || !a->fused_qk), "attn_decode_mma: kept first tokens beside a window come with the head norm as a kernel of its own");
     TB_REQUIRE(dtype == TB_BF16, "attn_decode_mma: bfloat16 only");
     TB_REQUIRE(a->hd == 64 || a->hd == 128, "attn_decode_mma: head_dim %d is not 64 or 128", a->hd);
@@ -854,6 +855,7 @@ static int launch_prefill(const CUtensorMap& map, const CUtensorMap& kv_map, con
 // sequence of the step starts at position 0, so all keys are among the step's own rows) or TB_KV_FROM_CACHE (keys
 // and values from the pages of a cache that keeps every key, the step's own appended already).
 extern "C" int tb_attn_prefill_mma_check(const AttnArgs* a, int dtype, int source) {
+    TB_REQUIRE(!(a->softcap > 0.f) && !a->rel_bias && !a->head_mix && !a->head_gate, "attn_prefill_mma: capped, biased, mixed or gated scores run on the mixed-heads kernels");
     TB_REQUIRE(a->keep_first >= 0, "attn_prefill_mma: a negative count of kept tokens");
     TB_REQUIRE(dtype == TB_BF16, "attn_prefill_mma: bfloat16 only");
     TB_REQUIRE(source == TB_KV_FROM_STEP || source == TB_KV_FROM_CACHE, "attn_prefill_mma: a sequence continues from the cache and its keys are not all there");

@@ -374,6 +374,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_c
 // TB_KV_FROM_CACHE (2): they are read from the cache's pages, where the step's own keys already lie (a cache
 // that keeps every key: no ring).
 extern "C" int tb_attn_prefill_tc_check(const AttnArgs* a, int dtype, int source) {
+    TB_REQUIRE(!(a->softcap > 0.f) && !a->rel_bias && !a->head_mix && !a->head_gate, "attn_prefill_tc: capped, biased, mixed or gated scores run on the mixed-heads kernels");
     TB_REQUIRE(a->keep_first >= 0, "attn_prefill_tc: a negative count of kept tokens");
     TB_REQUIRE(dtype == TB_BF16, "attn_prefill_tc: bfloat16 only");
     TB_REQUIRE(source == TB_KV_FROM_STEP || source == TB_KV_FROM_CACHE, "attn_prefill_tc: a sequence continues from the cache and its keys are not all there");

@@ -29,6 +29,7 @@ struct LatentArgs {
     const int* pos_of; const int* seq_of; const int* slot_of_seq; const int* kv_len;
     TbKvView cache; int append; int T;
     void* q_full; int qf_stride;            // if set: [T][qf_stride], head h at h * (dn + rd) as [unrotated dn | rotated rd]; q_nope and q_abs are not written
+    const float* kv_in;                     // where the first row's r + rd latent and key columns start, if not right behind the query columns (rows in_stride apart)
 };
 
 namespace {
@@ -83,7 +84,7 @@ __global__ void __launch_bounds__(128) latent_prep_kernel(LatentArgs a) {
         }
     }
     if (!a.owner) return;
-    const float* lat = row + a.H * qw;
+    const float* lat = a.kv_in ? a.kv_in + (size_t)t * a.in_stride : row + a.H * qw;
     float ss = 0.f;
     for (int i = threadIdx.x; i < a.r; i += blockDim.x) ss += lat[i] * lat[i];
     ss = block_sum(ss, red);
@@ -124,7 +125,7 @@ extern "C" int tb_latent_prep(const LatentArgs* args, int out_dtype, cudaStream_
     TB_REQUIRE(a.dk >= a.r + a.rd && a.dk % 8 == 0, "latent_prep: a row of %d elements for %d + %d (a multiple of 8 that holds both)", a.dk, a.r, a.rd);
     TB_REQUIRE(a.rope.rot >= 0 && a.rope.rot % 2 == 0 && a.rope.rot <= a.rd, "latent_prep: %d rotated dimensions of %d", a.rope.rot, a.rd);
     TB_REQUIRE(a.in && (a.q_full || (a.q_nope && a.q_abs)), "latent_prep: missing buffers");
-    TB_REQUIRE(a.in_stride >= a.H * (a.dn + a.rd) + (a.owner ? a.r + a.rd : 0), "latent_prep: the projection row is too short");
+    TB_REQUIRE(a.in_stride >= a.H * (a.dn + a.rd) + ((a.owner && !a.kv_in) ? a.r + a.rd : 0), "latent_prep: the projection row is too short");
     TB_REQUIRE(!a.owner || a.latent_w, "latent_prep: the latent's norm weight is missing");
     TB_REQUIRE(!a.append || (a.owner && a.cache.storage && a.cache.head_dim == a.dk && a.cache.kv_heads == 1), "latent_prep: the cache view does not match the rows");
     const size_t smem = (size_t)(a.rope.rot + 2) * sizeof(float);

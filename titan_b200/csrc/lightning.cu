@@ -12,7 +12,10 @@
 //                     add their parts of o with two shuffles.  Tokens are staged in shared memory sixteen at a time,
 //                     the next sixteen requested while these are worked through.
 // tb_gated_rmsnorm    y = o / sqrt(mean(o^2) + eps) * w * sigmoid(g) over the concatenated heads, one block a token.
+// tb_rotary_rows      rotates heads that lie side by side in float32 rows, in place, and scales some of them: what the
+//                     retention mixer does to q and k between its projection and this recurrence (LightningArgs.plain).
 #include "common.cuh"
+#include "qk_args.h"
 
 struct LightningArgs {
     const void* proj; int stride;           // [T][stride]: q (H*dk) | k (H*dk) | v (H*dv) | g (H*dv), compute dtype
@@ -22,6 +25,7 @@ struct LightningArgs {
     const int* q_start; const int* slot_of_seq;
     int B; int H; int dk; int dv;
     int max_new;                            // most tokens a sequence brings in this step (1: a step of single tokens)
+    int plain;                              // 1: q, k and v enter the recurrence as they stand in the rows (no silu): the retention mixer, whose rows are float32
 };
 
 namespace {
@@ -91,7 +95,7 @@ __global__ void __launch_bounds__(128) lightning_scan_kernel(LightningArgs a) {
             const int e = tid + 128 * u;
             bool real;
             source(u, c0, &real);
-            if (e < CH * ROW) sm[e] = real ? silu_f(stage[u]) : 0.f;
+            if (e < CH * ROW) sm[e] = real ? (a.plain ? stage[u] : silu_f(stage[u])) : 0.f;
         }
         __syncthreads();
         if (c0 + CH < t1) request(c0 + CH);
@@ -207,7 +211,7 @@ __global__ void __launch_bounds__(128) lightning_scan_vec_kernel(LightningArgs a
                 float v[8];
                 stage[u].get(v);
 #pragma unroll
-                for (int i = 0; i < 8; ++i) v[i] = real ? silu_f(v[i]) : 0.f;
+                for (int i = 0; i < 8; ++i) v[i] = real ? (a.plain ? v[i] : silu_f(v[i])) : 0.f;
                 *reinterpret_cast<float4*>(sm + to) = make_float4(v[0], v[1], v[2], v[3]);
                 *reinterpret_cast<float4*>(sm + to + 4) = make_float4(v[4], v[5], v[6], v[7]);
             }
@@ -258,6 +262,39 @@ __global__ void gated_rmsnorm_kernel(const float* __restrict__ o, int ldo, const
     for (int i = threadIdx.x; i < N; i += blockDim.x) {
         const float g = ldf(gate + t * ldg + i);
         stf(y + t * ldy + i, row[i] * scale * w[i] * (1.0f / (1.0f + expf(-g))));
+    }
+}
+
+// One block a token; a thread takes pairs of one head's rotated dimensions (both members, so the rotation is in place),
+// then the elements that pass unrotated.  Heads from ``scale_from`` on are multiplied by ``scale`` after the rotation.
+__global__ void __launch_bounds__(128) rotary_rows_kernel(float* x, int stride, const int* __restrict__ pos_of, int heads, int hd,
+                                                          TbRotary rope, int scale_from, float scale) {
+    pdl_launch_dependents();
+    pdl_wait();
+    extern __shared__ float cs[];           // [half] cosines, [half] sines
+    const int t = blockIdx.x, half = rope.rot >> 1;
+    float* sn = cs + half;
+    const float p = (float)pos_of[t] + rope.offset;
+    for (int k = threadIdx.x; k < half; k += blockDim.x) {
+        float sv, cv;
+        sincosf(p * rope.inv_freq[k], &sv, &cv);
+        sn[k] = sv * rope.magnitude; cs[k] = cv * rope.magnitude;
+    }
+    __syncthreads();
+    float* row = x + (size_t)t * stride;
+    const int per = half + (hd - rope.rot);          // work items a head: pairs, then single elements
+    for (int i = threadIdx.x; i < heads * per; i += blockDim.x) {
+        const int h = i / per, w = i % per;
+        float* head = row + (size_t)h * hd;
+        const float f = h >= scale_from ? scale : 1.f;
+        if (w < half) {
+            const int ia = rope.adjacent ? 2 * w : w, ib = rope.adjacent ? 2 * w + 1 : w + half;
+            const float u = head[ia], v = head[ib];
+            head[ia] = (u * cs[w] - v * sn[w]) * f;
+            head[ib] = (v * cs[w] + u * sn[w]) * f;
+        } else {
+            head[rope.rot + (w - half)] *= f;
+        }
     }
 }
 
@@ -337,5 +374,14 @@ extern "C" int tb_gated_rmsnorm(const float* o, int ldo, const float* w, const v
     else if (dtype == TB_BF16) tb_launch(gated_rmsnorm_kernel<__nv_bfloat16>, n_rows, threads, 0, stream, o, ldo, w, (const __nv_bfloat16*)gate, ldg, (__nv_bfloat16*)y, ldy, N, eps);
     else TB_REQUIRE(false, "gated_rmsnorm: unknown dtype %d", dtype);
     TB_CHECK_LAUNCH("gated_rmsnorm");
+    return 0;
+}
+
+extern "C" int tb_rotary_rows(float* x, int stride, const int* pos_of, int n_rows, int heads, int hd, const TbRotary* rope, int scale_from,
+                              float scale, cudaStream_t stream) {
+    TB_REQUIRE(x && pos_of && rope && n_rows > 0 && heads > 0 && hd > 0 && stride >= heads * hd, "rotary_rows: rows of heads are wanted");
+    TB_REQUIRE(rope->inv_freq && rope->rot > 0 && rope->rot % 2 == 0 && rope->rot <= hd, "rotary_rows: %d rotated dimensions of a head of %d", rope->rot, hd);
+    tb_launch(rotary_rows_kernel, n_rows, 128, (size_t)rope->rot * sizeof(float), stream, x, stride, pos_of, heads, hd, *rope, scale_from, scale);
+    TB_CHECK_LAUNCH("rotary_rows");
     return 0;
 }

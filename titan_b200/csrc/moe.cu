@@ -84,9 +84,13 @@ __global__ void __launch_bounds__(128) moe_route_kernel(const float* __restrict_
 // and only inside the ``keep`` groups (of n_all / groups neighbours each) whose best such score is largest; the weights
 // are the chosen experts' s over their sum (+ 1e-20).  One warp a token; the lowest index wins a tie.  ``score`` and
 // ``choice`` are the warp's rows in shared memory.
+// ``sigmoid``: the scores are sigmoids of the router's outputs, each on its own, instead of a softmax over the row.
+// ``group_best``: a group's score is the sum of its ``group_best`` largest choice scores (1: its best one).  ``renorm`` 0:
+// the weights are the chosen experts' scores as they are, not divided by their sum.
 __global__ void __launch_bounds__(128) moe_route_all_kernel(const float* __restrict__ z, int ldz, int n_all, int top,
                                                             const float* __restrict__ correction, int groups, int keep,
-                                                            int* __restrict__ ids, float* __restrict__ wts, int T_) {
+                                                            int* __restrict__ ids, float* __restrict__ wts, int T_,
+                                                            int sigmoid, int group_best, int renorm) {
     pdl_launch_dependents();
     pdl_wait();
     extern __shared__ float sm[];           // per warp: n_all scores, n_all choice scores, ``groups`` group scores and as many marks
@@ -98,14 +102,21 @@ __global__ void __launch_bounds__(128) moe_route_all_kernel(const float* __restr
     float* best_of = choice + n_all;
     float* kept = best_of + groups;
     const float* row = z + (size_t)t * ldz;
-    float m = -FLT_MAX;
-    for (int e = lane; e < n_all; e += 32) m = fmaxf(m, row[e]);
-    m = warp_max(m);
-    float sum = 0.f;
-    for (int e = lane; e < n_all; e += 32) { const float p = expf(row[e] - m); score[e] = p; sum += p; }
-    sum = warp_sum(sum);
-    const float inv = 1.0f / sum;
-    for (int e = lane; e < n_all; e += 32) { score[e] *= inv; choice[e] = score[e] + (correction ? correction[e] : 0.f); }
+    if (sigmoid) {
+        for (int e = lane; e < n_all; e += 32) {
+            score[e] = 1.0f / (1.0f + expf(-row[e]));
+            choice[e] = score[e] + (correction ? correction[e] : 0.f);
+        }
+    } else {
+        float m = -FLT_MAX;
+        for (int e = lane; e < n_all; e += 32) m = fmaxf(m, row[e]);
+        m = warp_max(m);
+        float sum = 0.f;
+        for (int e = lane; e < n_all; e += 32) { const float p = expf(row[e] - m); score[e] = p; sum += p; }
+        sum = warp_sum(sum);
+        const float inv = 1.0f / sum;
+        for (int e = lane; e < n_all; e += 32) { score[e] *= inv; choice[e] = score[e] + (correction ? correction[e] : 0.f); }
+    }
     __syncwarp();
     auto arg_max = [&](const float* v, int n, float* best_out) -> int {
         float best = -INFINITY; int at = 0x7fffffff;
@@ -123,9 +134,26 @@ __global__ void __launch_bounds__(128) moe_route_all_kernel(const float* __restr
     if (groups > 1 && keep < groups) {
         const int per = n_all / groups;
         for (int g = lane; g < groups; g += 32) {
-            float b = -INFINITY;
-            for (int e = g * per; e < (g + 1) * per; ++e) b = fmaxf(b, choice[e]);
-            best_of[g] = b;
+            if (group_best <= 1) {
+                float b = -INFINITY;
+                for (int e = g * per; e < (g + 1) * per; ++e) b = fmaxf(b, choice[e]);
+                best_of[g] = b;
+            } else {                        // the sum of the group's largest few: one pass a rank, below the one before (ties by index)
+                float total = 0.f, last = INFINITY;
+                int last_at = -1;
+                for (int k = 0; k < group_best && k < per; ++k) {
+                    float b = -INFINITY;
+                    int at = -1;
+                    for (int e = g * per; e < (g + 1) * per; ++e) {
+                        const float c = choice[e];
+                        const bool below = c < last || (c == last && e > last_at);
+                        if (below && c > b) { b = c; at = e; }
+                    }
+                    if (at < 0) break;
+                    total += b; last = b; last_at = at;
+                }
+                best_of[g] = total;
+            }
         }
         __syncwarp();
         for (int g = lane; g < groups; g += 32) kept[g] = 0.f;
@@ -152,6 +180,7 @@ __global__ void __launch_bounds__(128) moe_route_all_kernel(const float* __restr
         if (lane == 0) { ids[(size_t)t * top + k] = e; wts[(size_t)t * top + k] = w; choice[e] = -INFINITY; }
         __syncwarp();
     }
+    if (!renorm) return;
     const float norm = 1.0f / (total + 1e-20f);
     for (int k = lane; k < top; k += 32) wts[(size_t)t * top + k] *= norm;
 }
@@ -378,14 +407,25 @@ extern "C" int tb_moe_route(const float* z, int ldz, int E, int top, int has_gat
     return 0;
 }
 
+extern "C" int tb_moe_route_scored(const float* z, int ldz, int n_all, int top, const float* correction, int groups, int keep,
+                                   int* ids, float* wts, int T_, int sigmoid, int group_best, int renorm, cudaStream_t stream);
+
 extern "C" int tb_moe_route_all(const float* z, int ldz, int n_all, int top, const float* correction, int groups, int keep,
                                 int* ids, float* wts, int T_, cudaStream_t stream) {
+    return tb_moe_route_scored(z, ldz, n_all, top, correction, groups, keep, ids, wts, T_, 0, 1, 1, stream);
+}
+
+// The same choice with the scores' kind (softmax over the row, or a sigmoid an output), the number of a group's best choice
+// scores that make the group's score, and whether the chosen weights are divided by their sum, as arguments.
+extern "C" int tb_moe_route_scored(const float* z, int ldz, int n_all, int top, const float* correction, int groups, int keep,
+                                   int* ids, float* wts, int T_, int sigmoid, int group_best, int renorm, cudaStream_t stream) {
+    TB_REQUIRE(group_best >= 1, "moe_route_all: a group's score is the sum of at least one of its experts' scores");
     TB_REQUIRE(T_ > 0 && n_all > 0 && top > 0 && top <= n_all && n_all <= 2048, "moe_route_all: %d of %d experts (at most 2048)", top, n_all);
     TB_REQUIRE(groups > 0 && keep > 0 && keep <= groups && n_all % groups == 0, "moe_route_all: %d groups of which %d are kept, over %d experts", groups, keep, n_all);
     TB_REQUIRE(top <= keep * (n_all / groups), "moe_route_all: %d experts a token out of %d groups of %d", top, keep, n_all / groups);
     TB_REQUIRE(ldz >= n_all && z && ids && wts, "moe_route_all: missing buffers");
     tb_launch(moe_route_all_kernel, (T_ + 3) / 4, 128, (size_t)4 * (2 * n_all + 2 * groups) * sizeof(float), stream, z, ldz, n_all, top, correction,
-              groups, keep, ids, wts, T_);
+              groups, keep, ids, wts, T_, sigmoid, group_best, renorm);
     TB_CHECK_LAUNCH("moe_route_all");
     return 0;
 }

@@ -88,7 +88,9 @@ class AttnArgs(Structure):
                 ("nh", c_int), ("nkv", c_int), ("hd", c_int), ("window", c_int), ("scale", c_float),
                 ("chunk", c_int), ("n_splits", c_int), ("scratch", c_void_p),
                 ("early_len", c_void_p), ("early_mode", c_int), ("fused_qk", POINTER(QkArgs)),
-                ("hd_v", c_int), ("v_alias", c_int), ("head_blocks", c_int), ("sink", c_void_p), ("keep_first", c_int)]
+                ("hd_v", c_int), ("v_alias", c_int), ("head_blocks", c_int), ("sink", c_void_p), ("keep_first", c_int),
+                ("softcap", c_float), ("rel_bias", c_void_p), ("rel_far", c_int), ("head_mix", c_void_p),
+                ("head_gate", c_void_p), ("head_gate_stride", c_int)]
 
 
 class LatentArgs(Structure):
@@ -98,7 +100,7 @@ class LatentArgs(Structure):
                 ("latent_w", c_void_p), ("eps", c_float), ("rope", RotaryArgs),
                 ("H", c_int), ("dn", c_int), ("rd", c_int), ("r", c_int), ("dk", c_int), ("owner", c_int),
                 ("pos_of", c_void_p), ("seq_of", c_void_p), ("slot_of_seq", c_void_p), ("kv_len", c_void_p),
-                ("cache", KvView), ("append", c_int), ("T", c_int), ("q_full", c_void_p), ("qf_stride", c_int)]
+                ("cache", KvView), ("append", c_int), ("T", c_int), ("q_full", c_void_p), ("qf_stride", c_int), ("kv_in", c_void_p)]
 
 
 class SplitAttnArgs(Structure):
@@ -112,7 +114,18 @@ class LightningArgs(Structure):
     """Arguments of the decayed linear-attention recurrence (csrc/lightning.cu)."""
     _fields_ = [("proj", c_void_p), ("stride", c_int), ("out", c_void_p), ("out_stride", c_int), ("state", c_void_p),
                 ("decay", c_void_p), ("q_start", c_void_p), ("slot_of_seq", c_void_p),
-                ("B", c_int), ("H", c_int), ("dk", c_int), ("dv", c_int), ("max_new", c_int)]
+                ("B", c_int), ("H", c_int), ("dk", c_int), ("dv", c_int), ("max_new", c_int), ("plain", c_int)]
+
+
+class WholeNormArgs(Structure):
+    """Arguments of the kernel between a fused Q | K | V projection with biases and attention whose queries and keys are
+    normed over the whole projection (csrc/attention_mixed.cu: tb_qkv_whole_norm)."""
+    _fields_ = [("inp", c_void_p), ("in_stride", c_int), ("bias", c_void_p), ("q_w", c_void_p), ("k_w", c_void_p), ("eps", c_float),
+                ("q_count", c_int), ("k_count", c_int), ("q_out", c_void_p), ("q_stride", c_int), ("kv_out", c_void_p), ("kv_stride", c_int),
+                ("nh", c_int), ("nkv", c_int), ("hd", c_int),
+                ("pos_of", c_void_p), ("seq_of", c_void_p), ("slot_of_seq", c_void_p), ("kv_len", c_void_p),
+                ("cache", KvView), ("append", c_int), ("T", c_int),
+                ("o_bias", c_void_p), ("o_out", c_void_p), ("o_stride", c_int), ("o_width", c_int)]
 
 
 class WkvArgs(Structure):
@@ -186,6 +199,13 @@ def lib():
         l.tb_delta_prep.argtypes = [POINTER(DeltaPrepArgs), c_int, c_void_p]
         l.tb_recurrent_scan.argtypes = [POINTER(ScanArgs), c_int, c_int, c_void_p]
         l.tb_moe_route_all.argtypes = [c_void_p, c_int, c_int, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p]
+        l.tb_moe_route_scored.argtypes = [c_void_p, c_int, c_int, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p]
+        l.tb_group_rmsnorm.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_float, c_void_p]
+        l.tb_residual_group_norm.argtypes = [c_void_p, c_float, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float, c_void_p]
+        l.tb_qkv_whole_norm.argtypes = [POINTER(WholeNormArgs), c_int, c_void_p]
+        l.tb_attn_mixed_prefill.argtypes = [POINTER(AttnArgs), c_int, c_void_p]
+        l.tb_attn_mixed_decode.argtypes = [POINTER(AttnArgs), c_int, c_void_p]
+        l.tb_rotary_rows.argtypes = [c_void_p, c_int, c_void_p, c_int, c_int, c_int, POINTER(RotaryArgs), c_int, c_float, c_void_p]
         l.tb_gemm_simt_batched.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
                                            c_longlong, c_longlong, c_longlong, c_void_p]
         l.tb_gemm_rows.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p]
@@ -481,6 +501,57 @@ def moe_route_all(z: torch.Tensor, top: int, correction: Optional[torch.Tensor],
     _need_cuda(z, correction, ids, wts)
     _check(lib().tb_moe_route_all(z.data_ptr(), z.stride(0), z.shape[1], top, _ptr(correction), groups, keep, ids.data_ptr(), wts.data_ptr(),
                                   z.shape[0], stream))
+
+
+def moe_route_scored(z: torch.Tensor, top: int, correction: Optional[torch.Tensor], groups: int, keep: int, ids: torch.Tensor,
+                     wts: torch.Tensor, stream: int, sigmoid: bool, group_best: int, renorm: bool) -> None:
+    """``moe_route_all`` with its three fixed choices as arguments: scores by a sigmoid an output instead of a softmax over the
+    row; a group's score as the sum of its ``group_best`` largest choice scores; weights left as the chosen scores."""
+    _need_cuda(z, correction, ids, wts)
+    _check(lib().tb_moe_route_scored(z.data_ptr(), z.stride(0), z.shape[1], top, _ptr(correction), groups, keep, ids.data_ptr(), wts.data_ptr(),
+                                     z.shape[0], int(sigmoid), int(group_best), int(renorm), stream))
+
+
+def group_rmsnorm(x: torch.Tensor, w: torch.Tensor, y: torch.Tensor, groups: int, eps: float, stream: int,
+                  rows: Optional[torch.Tensor] = None) -> None:
+    """RMS norm of float32 rows in ``groups`` equal runs, each with its own mean square, one weight over the row."""
+    _need_cuda(x, w, y, rows)
+    if x.dtype != torch.float32 or not x.is_contiguous() or not y.is_contiguous():
+        raise KernelError("group_rmsnorm: contiguous float32 rows are wanted")
+    _check(lib().tb_group_rmsnorm(x.data_ptr(), w.data_ptr(), y.data_ptr(), dtype_code(y.dtype), _ptr(rows), y.shape[0], x.shape[-1],
+                                  groups, eps, stream))
+
+
+def residual_group_norm(y: torch.Tensor, mult: float, x: torch.Tensor, stream: int, norm_w: Optional[torch.Tensor] = None, groups: int = 1,
+                        eps: float = 0.0, h: Optional[torch.Tensor] = None) -> None:
+    """x += mult * y (float32 rows), y left zeroed; with ``h``: h = the grouped RMS norm of the NEW rows times norm_w, in h's dtype."""
+    _need_cuda(y, x, norm_w, h)
+    if y.dtype != torch.float32 or x.dtype != torch.float32 or y.shape != x.shape or not (y.is_contiguous() and x.is_contiguous()) \
+            or (h is not None and (h.shape != x.shape or not h.is_contiguous() or norm_w is None)):
+        raise KernelError("residual_group_norm: contiguous float32 rows of one shape are wanted")
+    _check(lib().tb_residual_group_norm(y.data_ptr(), float(mult), x.data_ptr(), _ptr(norm_w), _ptr(h),
+                                        dtype_code(h.dtype) if h is not None else F32, x.shape[0], x.shape[1], groups, eps, stream))
+
+
+def qkv_whole_norm(args: "WholeNormArgs", out_dtype: torch.dtype, stream: int) -> None:
+    _check(lib().tb_qkv_whole_norm(byref(args), dtype_code(out_dtype), stream))
+
+
+def attn_mixed_prefill(args: AttnArgs, dtype: torch.dtype, stream: int) -> None:
+    _check(lib().tb_attn_mixed_prefill(byref(args), dtype_code(dtype), stream))
+
+
+def attn_mixed_decode(args: AttnArgs, dtype: torch.dtype, stream: int) -> None:
+    _check(lib().tb_attn_mixed_decode(byref(args), dtype_code(dtype), stream))
+
+
+def rotary_rows(x: torch.Tensor, pos_of: torch.Tensor, heads: int, hd: int, rope: RotaryArgs, scale_from: int, scale: float, stream: int) -> None:
+    """Rotates ``heads`` heads of ``hd`` elements that lie side by side from column 0 of the float32 rows ``x``, in place, by the
+    rows' positions; heads from ``scale_from`` on are multiplied by ``scale`` afterwards."""
+    _need_cuda(x, pos_of)
+    if x.dtype != torch.float32 or x.stride(-1) != 1:
+        raise KernelError("rotary_rows: float32 rows are wanted")
+    _check(lib().tb_rotary_rows(x.data_ptr(), x.stride(0), pos_of.data_ptr(), x.shape[0], heads, hd, byref(rope), scale_from, scale, stream))
 
 
 def round_rows(x: torch.Tensor, out: torch.Tensor, stream: int) -> None:

@@ -6,7 +6,7 @@ from typing import List
 from ..weights.loader import WeightSpec
 from .base import (BLOCKS, FEED_FORWARDS, MIXERS, NORMS, POSITIONS, FeedForward, Mixer, Norm, Part,
                    PositionEncoding, Registry)
-from . import attention, block, gated_delta, latent_attention, lightning, mlp, mlstm, moe, norm, parallel, rotary, token_table, wkv  # noqa: F401  (registration)
+from . import attention, block, gated_delta, latent_attention, lightning, mlp, mlstm, moe, norm, parallel, retention, rotary, token_table, wkv  # noqa: F401  (registration)
 
 
 def build_block(layer_spec):

@@ -38,6 +38,18 @@ Options of the spec (``MixerSpec.extra``) beyond the common fields:
   mixer's own input, before the output projection.
 * ``output_scale``: a factor on what the mixer adds to the residual stream (a mixer that runs beside another); it is applied to
   the rows that enter the output projection, in float32 before they are rounded.
+* Scores shaped before the softmax, and what comes with them in the designs that do so (any of these sends the mixer to the
+  mixed-heads kernels, ``csrc/attention_mixed.cu``; no rotation, sink, kept tokens, head norm or blended values beside them):
+  ``bias`` = True: the q, k, v and o projections have biases, tensors ``<name>.b``.
+  ``whole_norm`` = (q weight name, k weight name, eps): ALL of a token's query elements are divided by one root mean square
+  (every head together), times a weight as wide as the projection; likewise the keys.
+  ``softcap`` = c: s <- c * tanh(s / c) after the scale.
+  ``rel_bias`` = (name, rows, far): a table [rows, heads]; the row for distance n = query position - key position is n itself
+  below rows/2, else min(rows - 1, rows/2 + floor(ln(n / (rows/2)) / ln(far / (rows/2)) * (rows - rows/2))), added to the
+  capped score, unscaled.  The mixer spreads the table by distance once, when the tensors are bound.
+  ``head_mix`` = name of a [heads, heads] tensor M: head h's score becomes sum_g M[h, g] * score_g, for every (query, key) pair,
+  before the softmax.
+  ``head_gate`` = name of a [heads, hidden] tensor: head h's output is multiplied by sigmoid(W h)_h, one number a head.
 * ``value_mix`` = (first, name): values are blended across layers.  ``first`` None: this layer's values are what the
   others blend with, and it keeps them for the step; else v <- (1 - l) v + l v_first with l the tensor ``name`` and
   v_first the values of layer ``first`` for the same tokens.  The blended values are what the cache holds.
@@ -87,6 +99,19 @@ def decode_split(lay, kv_heads: int, options, fast: bool):
     return int(options.get("attn_min_chunk", 128)), forced or splits
 
 
+def distance_rows(rows: int, far: float) -> List[int]:
+    """Row of a distance table of ``rows`` rows for every distance 0 .. ceil(far): the distance itself below rows/2, then
+    logarithmic steps that reach the last row at ``far`` (every larger distance reads the last row too)."""
+    half = rows // 2
+    out = []
+    for n in range(int(math.ceil(far)) + 1):
+        if n < half or half == 0:
+            out.append(min(n, rows - 1))
+        else:
+            out.append(min(rows - 1, half + int(math.floor(math.log(n / half) / math.log(far / half) * (rows - half)))))
+    return out
+
+
 class AttentionMixer(Mixer):
     folds_norm = True           # a decode step's Q|K|V product takes the norm before it in
 
@@ -132,6 +157,28 @@ class AttentionMixer(Mixer):
             raise ValueError(f"{s.position.rotary_dim} rotated dimensions in a head of {self.key_dim}")
         self.w_qkv = self.w_o = self.q_norm = self.k_norm = None
         self._views = {}
+        # scores shaped before the softmax, biases, norms over the whole projection, one gate a head
+        self.has_bias = bool(s.option("bias", False))
+        self.whole_norm = s.option("whole_norm")
+        self.softcap = float(s.option("softcap", 0.0) or 0.0)
+        self.rel_spec = s.option("rel_bias")
+        self.mix_name, self.head_gate_name = s.option("head_mix"), s.option("head_gate")
+        self.shaped = bool(self.has_bias or self.whole_norm or self.softcap or self.rel_spec or self.mix_name or self.head_gate_name)
+        if self.shaped:
+            self.folds_norm = False
+            if (self.shared or self.sink_name or self.keep_first or self.unit_norm or self.value_mix is not None or self.value_norm is not None
+                    or self.gate_name or s.qk_norm is not None or s.position.kind != "none" or self.output_scale != 1.0):
+                raise ValueError("shaped scores, biases, whole-projection norms and a gate a head come without rotation, sink, kept tokens, "
+                                 "head norms, normed or blended values, an element-wise gate, an output factor or another layer's cache")
+            if s.num_heads > 32:
+                raise ValueError(f"{s.num_heads} heads whose scores are blended: the kernel takes up to 32")
+            if self.softcap < 0:
+                raise ValueError("softcap must be positive")
+            if self.rel_spec is not None:
+                _, rows, far = self.rel_spec
+                if rows < 1 or (rows >= 2 and not far > rows // 2):
+                    raise ValueError(f"a distance table of {rows} rows that reaches its last row at distance {far}")
+        self.bias = self.b_o = self.whole_q_w = self.whole_k_w = self.rel_table = self.head_mix = None
 
     # -- declaration ------------------------------------------------------ #
     def cache_need(self) -> Optional[CacheNeed]:
@@ -171,6 +218,20 @@ class AttentionMixer(Mixer):
         if s.qk_norm is not None:
             for which in ("q",) if self.shared else ("q", "k"):
                 specs.append(WeightSpec(p + s.qk_norm.weight.format(which), (s.head_dim,), "vector", ("one_plus_normal", 0.1)))
+        if self.has_bias:
+            specs += [WeightSpec(p + n["q"] + ".b", (s.num_heads * kd,), "vector", ("normal", 0.1)),
+                      WeightSpec(p + n["k"] + ".b", (s.num_kv_heads * kd,), "vector", ("normal", 0.1)),
+                      WeightSpec(p + n["v"] + ".b", (s.num_kv_heads * vd,), "vector", ("normal", 0.1)),
+                      WeightSpec(p + n["o"] + ".b", (s.hidden_size,), "vector", ("normal", 0.1))]
+        if self.whole_norm:
+            specs += [WeightSpec(p + self.whole_norm[0], (s.num_heads * kd,), "vector", ("one_plus_normal", 0.1)),
+                      WeightSpec(p + self.whole_norm[1], (s.num_kv_heads * kd,), "vector", ("one_plus_normal", 0.1))]
+        if self.rel_spec is not None:
+            specs.append(WeightSpec(p + self.rel_spec[0], (int(self.rel_spec[1]), s.num_heads), "vector", ("normal", 0.5)))
+        if self.mix_name:
+            specs.append(WeightSpec(p + self.mix_name, (s.num_heads, s.num_heads), "vector", ("normal_around", 0.1, 1.0 / s.num_heads)))
+        if self.head_gate_name:
+            specs.append(WeightSpec(p + self.head_gate_name, (s.num_heads, s.hidden_size)))
         return specs
 
     def bind(self, get) -> None:
@@ -196,6 +257,32 @@ class AttentionMixer(Mixer):
         if s.qk_norm is not None:
             self.q_norm = get(p + s.qk_norm.weight.format("q"))
             self.k_norm = None if self.shared else get(p + s.qk_norm.weight.format("k"))
+        if self.shaped:
+            dev = self.w_o.device
+            if self.has_bias:
+                self.bias = torch.cat([self._padded_vec(get(p + n["q"] + ".b"), s.num_heads, self.key_dim),
+                                       self._padded_vec(get(p + n["k"] + ".b"), s.num_kv_heads, self.key_dim),
+                                       self._padded_vec(get(p + n["v"] + ".b"), s.num_kv_heads, self.value_dim)]).float().contiguous()
+                self.b_o = get(p + n["o"] + ".b").float().contiguous()
+            if self.whole_norm:
+                self.whole_q_w = self._padded_vec(get(p + self.whole_norm[0]), s.num_heads, self.key_dim).float().contiguous()
+                self.whole_k_w = self._padded_vec(get(p + self.whole_norm[1]), s.num_kv_heads, self.key_dim).float().contiguous()
+            if self.rel_spec is not None:              # the table spread by distance: row n for distance n, the last row for every larger one
+                name, rows, far = self.rel_spec
+                index = torch.tensor(distance_rows(int(rows), float(far)), dtype=torch.long, device=dev)
+                self.rel_table = get(p + name).float().index_select(0, index).contiguous()
+            if self.mix_name:
+                self.head_mix = get(p + self.mix_name).float().contiguous()
+            if self.head_gate_name:                    # one more block of the fused projection: the heads' gate logits, padded to whole 32 bytes
+                g = get(p + self.head_gate_name)
+                pad = -(-s.num_heads // 8) * 8 - s.num_heads
+                self.w_qkv = torch.cat([self.w_qkv, g, g.new_zeros((pad, g.shape[1]))], dim=0).contiguous()
+
+    def _padded_vec(self, v: torch.Tensor, heads: int, dim: int) -> torch.Tensor:
+        """A vector over heads of ``dim`` elements as one over heads of ``self.hd``, the new elements zero."""
+        if dim == self.hd:
+            return v
+        return torch.nn.functional.pad(v.reshape(heads, dim), (0, self.hd - dim)).reshape(heads * self.hd).contiguous()
 
     def _padded_rows(self, w: torch.Tensor, heads: int, dim: int) -> torch.Tensor:
         """A projection whose heads are ``dim`` wide as one whose heads are ``self.hd`` wide, the new rows zero."""
@@ -237,7 +324,67 @@ class AttentionMixer(Mixer):
         qa.kv_len = lay.kv_len.data_ptr()
         return qa
 
+    def _forward_shaped(self, h, ctx, cache, out: torch.Tensor) -> None:
+        """Biases, norms over the whole projection, shaped and blended scores, one gate a head: one float32 product
+        (Q | K | V | gate logits), the kernel that adds biases, norms, rounds and appends, the mixed-heads attention, the
+        output projection."""
+        s, lay = self.spec, ctx.layout
+        T, Q, KV, hd = lay.T, self.Q, self.KV, self.hd
+        view = self._view(cache)
+        decode = lay.all_single
+        width = self.w_qkv.shape[0]
+        proj = ctx.empty((T, width), torch.float32)
+        linear.matmul(rows_of(h), self.w_qkv, proj, linear.EPI_F32, ctx)
+        q_buf = ctx.empty((T, Q))
+        kv_rows = None if decode else ctx.empty((T, 2 * KV))
+        append_now = decode or view.ring_rows == 0 or lay.all_fresh
+        wa = K.WholeNormArgs()
+        wa.inp, wa.in_stride = proj.data_ptr(), width
+        wa.bias = None if self.bias is None else self.bias.data_ptr()
+        if self.whole_norm:
+            wa.q_w, wa.k_w, wa.eps = self.whole_q_w.data_ptr(), self.whole_k_w.data_ptr(), float(self.whole_norm[2])
+            wa.q_count, wa.k_count = s.num_heads * self.key_dim, s.num_kv_heads * self.key_dim
+        wa.q_out, wa.q_stride = q_buf.data_ptr(), Q
+        wa.kv_out, wa.kv_stride = (None, 0) if kv_rows is None else (kv_rows.data_ptr(), 2 * KV)
+        wa.nh, wa.nkv, wa.hd = s.num_heads, s.num_kv_heads, hd
+        wa.pos_of, wa.seq_of, wa.slot_of_seq, wa.kv_len = lay.pos_of.data_ptr(), lay.seq_of.data_ptr(), lay.slot_of_seq.data_ptr(), lay.kv_len.data_ptr()
+        wa.cache, wa.append, wa.T = view, int(append_now), T
+        if self.b_o is not None:
+            wa.o_bias, wa.o_out, wa.o_stride, wa.o_width = self.b_o.data_ptr(), out.data_ptr(), out.stride(0), s.hidden_size
+        K.qkv_whole_norm(wa, q_buf.dtype, ctx.stream)
+
+        attn = ctx.empty((T, Q))
+        aa = K.AttnArgs()
+        aa.q, aa.q_stride = q_buf.data_ptr(), Q
+        aa.out, aa.out_stride = attn.data_ptr(), Q
+        aa.cache, aa.batch = view, lay.c_struct()
+        aa.nh, aa.nkv, aa.hd = s.num_heads, view.kv_heads, hd
+        aa.window, aa.scale = s.window or 0, self.scale
+        aa.softcap = self.softcap
+        if self.rel_table is not None:
+            aa.rel_bias, aa.rel_far = self.rel_table.data_ptr(), self.rel_table.shape[0] - 1
+        aa.head_mix = None if self.head_mix is None else self.head_mix.data_ptr()
+        if self.head_gate_name:
+            aa.head_gate, aa.head_gate_stride = proj.data_ptr() + (Q + 2 * KV) * 4, width
+        if decode:
+            chunk, splits = decode_split(lay, view.kv_heads, ctx.options, False)
+            need = lay.B * s.num_heads * splits * (hd + 2)
+            scratch = ctx.scratch.get("attn_partials")
+            if scratch is None or scratch.numel() < need:
+                scratch = ctx.scratch["attn_partials"] = torch.empty(need, dtype=torch.float32, device=ctx.device)
+            aa.kv_new, aa.kv_stride = None, 0
+            aa.chunk, aa.n_splits, aa.scratch = chunk, splits, scratch.data_ptr()
+            K.attn_mixed_decode(aa, q_buf.dtype, ctx.stream)
+        else:
+            aa.kv_new, aa.kv_stride = kv_rows.data_ptr(), 2 * KV
+            K.attn_mixed_prefill(aa, q_buf.dtype, ctx.stream)
+            if not append_now:
+                K.kv_append(kv_rows, view, lay.c_struct(), ctx.stream)
+        linear.matmul(attn, self.w_o, out, linear.EPI_ADD, ctx)
+
     def forward(self, h, ctx, cache, out: torch.Tensor) -> None:
+        if self.shaped:
+            return self._forward_shaped(h, ctx, cache, out)
         s, lay = self.spec, ctx.layout
         T, Q, KV, hd = lay.T, self.Q, self.KV, self.hd
         width = Q if self.shared else Q + 2 * KV

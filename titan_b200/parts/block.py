@@ -4,7 +4,8 @@
 its first matrix product is handed over unevaluated (``norm.DeferredNorm``)
 (berniehans/titan: engine/engine-core/src/forward_cpu.rs:281-386).  The
 residual stream ``x`` is float32 and is updated in place: mixer and
-feed-forward add into it in the epilogue of their last matrix product.
+feed-forward add into it in the epilogue of their last matrix product.  The other arrangements (``pre_norm_scaled``,
+``output_norm``, ``hyper``, ``parallel``) are described at their classes.
 """
 from __future__ import annotations
 
@@ -45,7 +46,7 @@ class PreNormBlock(Part):
         deferred and the part can fold it into its first product."""
         # up to 16 rows: measured after 2,048-token prompts, folding gains 3 % of the step at 12 and 16 sequences and
         # loses 1 to 3 % at 20 to 32 (the kernels take up to 32 rows: twice the float32 rows per weight tile through L2)
-        if (getattr(consumer, "folds_norm", False) and hasattr(norm, "deferred") and ctx.options.get("fold_norms", True)
+        if (getattr(consumer, "folds_norm", False) and hasattr(norm, "deferred") and getattr(norm, "groups", 1) == 1 and ctx.options.get("fold_norms", True)
                 and x.shape[0] <= int(ctx.options.get("fold_norms_rows", 16))):
             return norm.deferred(x, ctx)
         return norm.forward(x, ctx)
@@ -148,6 +149,9 @@ class OutputNormBlock(Part):
         self.mixer_norm = NORMS.build(spec.mixer_norm)
         self.feed_forward = None if spec.feed_forward is None else FEED_FORWARDS.build(spec.feed_forward)
         self.feed_forward_norm = None if spec.feed_forward_norm is None else NORMS.build(spec.feed_forward_norm)
+        for n in (spec.mixer_norm, spec.feed_forward_norm) + tuple(spec.norms):
+            if n is not None and (n.kind != "rmsnorm" or getattr(n, "groups", 1) != 1):
+                raise ValueError("the output_norm arrangement folds a plain RMS norm (one group) into the kernel that adds a sublayer's output")
         more = tuple(spec.option("sublayers", ()))
         if len(more) != len(spec.norms):
             raise ValueError(f"{len(more)} further sublayers with {len(spec.norms)} norms")
@@ -229,8 +233,8 @@ class HyperConnectionBlock(Part):
         if self.streams < 1:
             raise ValueError("the hyper arrangement needs the number of streams")
         for n in (spec.mixer_norm, spec.feed_forward_norm):
-            if n is not None and n.kind != "rmsnorm":
-                raise ValueError("the hyper arrangement folds an RMS norm into the kernel that reads the streams")
+            if n is not None and (n.kind != "rmsnorm" or getattr(n, "groups", 1) != 1):
+                raise ValueError("the hyper arrangement folds a plain RMS norm (one group) into the kernel that reads the streams")
         self.spec, self.names = spec, names
         self.mixer_norm = NORMS.build(spec.mixer_norm)
         self.mixer = MIXERS.build(spec.mixer)
@@ -314,3 +318,59 @@ class HyperConnectionBlock(Part):
 
 
 BLOCKS.register("hyper", HyperConnectionBlock)
+
+
+class ParallelBlock(Part):
+    """``parallel``: ONE norm, and both sublayers read its output:
+
+        h = norm(x);   x += mult * (mixer(h) + feed_forward(h))
+
+    ``mult`` is ``LayerSpec.extra["residual_mult"]`` (1 if absent); the feed-forward may be absent.  Mixer and feed-forward
+    add into a zeroed float32 buffer of the step; one kernel then adds that buffer, times ``mult``, to the residual stream,
+    leaves it zeroed and, where the block that runs next is of this arrangement with an RMS norm (in groups or not), writes
+    that norm's rows, which the next block finds in ``ctx.carried``.  A layer runs one such kernel and, but for the first
+    layer of a step, no norm kernel of its own."""
+
+    def __init__(self, spec):
+        if spec.mixer_norm is None or spec.feed_forward_norm is not None or spec.norms:
+            raise ValueError("the parallel arrangement takes one norm (the mixer's), a mixer, and a feed-forward or none")
+        self.spec = spec
+        self.mult = float(spec.option("residual_mult", 1.0))
+        self.mixer_norm = NORMS.build(spec.mixer_norm)
+        self.mixer = MIXERS.build(spec.mixer)
+        self.feed_forward = None if spec.feed_forward is None else FEED_FORWARDS.build(spec.feed_forward)
+
+    def parts(self):
+        return (self.mixer_norm, self.mixer) + (() if self.feed_forward is None else (self.feed_forward,))
+
+    def weight_specs(self, prefix: str = "") -> List[WeightSpec]:
+        out: List[WeightSpec] = []
+        for part in self.parts():
+            out += part.weight_specs(self.spec.prefix)
+        return out
+
+    def bind(self, get) -> None:
+        for part in self.parts():
+            part.bind(lambda name: get(self.spec.prefix + name))
+
+    def forward(self, x: torch.Tensor, ctx, cache) -> None:
+        from .. import kernels as K
+        y = ctx.carried.get("sublayer_sum")
+        if y is None or y.shape != x.shape:
+            y = ctx.carried["sublayer_sum"] = torch.zeros_like(x)         # zeroed once a step; the joining kernel leaves it zeroed
+        kept = ctx.carried.pop("normed_rows", None)
+        h = kept[0] if kept is not None and kept[1] == ctx.run and kept[0].shape == x.shape else self.mixer_norm.forward(x, ctx)
+        self.mixer.forward(h, ctx, cache, y)
+        if self.feed_forward is not None:
+            self.feed_forward.forward(h, ctx, y)
+        nxt = ctx.next_block
+        following = nxt.mixer_norm if isinstance(nxt, ParallelBlock) and hasattr(nxt.mixer_norm, "groups") and ctx.options.get("fuse_parallel_norm", True) else None
+        if following is None:
+            K.residual_group_norm(y, self.mult, x, ctx.stream)
+            return
+        h = ctx.empty(tuple(x.shape))
+        K.residual_group_norm(y, self.mult, x, ctx.stream, norm_w=following.weight, groups=following.groups, eps=following.spec.eps, h=h)
+        ctx.carried["normed_rows"] = (h, ctx.run + 1)
+
+
+BLOCKS.register("parallel", ParallelBlock)

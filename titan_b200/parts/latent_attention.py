@@ -13,6 +13,11 @@ attends there with the cached row as key AND value (one "kv head" for all query 
     o~_h = sum_j p_hij c_j;   o_h = o~_h . U_v,h^T                    per head  [T, kv_rank] x [kv_rank, vdim]
     out += [o_1 .. o_H] . W_o^T
 
+With the option ``q_rank`` the queries go through a latent of their own: c_q = rmsnorm(h . W_dq^T) * w (``q_norm``, a
+NormSpec), q = c_q . W_uq^T (tensor roles "dq" and "uq" instead of "q"); the projection then yields [c_q_raw], [c_raw |
+k_raw] as two products (query latent; latent and key part), a norm kernel makes c_q, and a third product fills the query
+columns of the row that the prep kernel reads.
+
 Rows are padded with zeros to a multiple of 8 elements.  A mixer with ``cache_from`` has no W_dkv: it reads the rows
 of the named layer (its own window may be shorter than what that layer keeps).  A step of single tokens appends in
 the prep kernel and attends over the cache; a step with longer runs attends over cache + the step's own rows (the
@@ -57,6 +62,10 @@ class LatentAttentionMixer(Mixer):
         if self.position.rotary_dim > self.rd:
             raise ValueError(f"{self.position.rotary_dim} rotated dimensions of a part of {self.rd}")
         self.latent_norm_spec = s.option("latent_norm")
+        self.q_rank, self.q_norm_spec = int(s.option("q_rank", 0) or 0), s.option("q_norm")
+        if self.q_rank and self.q_norm_spec is None:
+            raise ValueError("queries through a latent need that latent's norm (q_norm)")
+        self.w_uq = self.q_norm = self.w_dkv = None
         self.scale = s.softmax_scale if s.softmax_scale is not None else 1.0 / math.sqrt(self.dn + self.rd)
         self.w_in = self.w_uk_t = self.w_uv = self.w_o = self.latent_w = None
         self._views = {}
@@ -69,12 +78,16 @@ class LatentAttentionMixer(Mixer):
 
     def _names(self):
         s = self.spec
-        return {role: s.name(role, role) for role in ("q", "dkv", "uk", "uv", "o")}
+        return {role: s.name(role, role) for role in ("q", "dq", "uq", "dkv", "uk", "uv", "o")}
 
     def weight_specs(self, prefix: str) -> List[WeightSpec]:
         s, p, n = self.spec, prefix + self.spec.prefix, self._names()
         W = s.hidden_size
-        specs = [WeightSpec(p + n["q"], (self.H * (self.dn + self.rd), W))]
+        if self.q_rank:
+            specs = [WeightSpec(p + n["dq"], (self.q_rank, W)), WeightSpec(p + n["uq"], (self.H * (self.dn + self.rd), self.q_rank))]
+            specs += NORMS.build(self.q_norm_spec).weight_specs(p)
+        else:
+            specs = [WeightSpec(p + n["q"], (self.H * (self.dn + self.rd), W))]
         if not self.shared:
             specs.append(WeightSpec(p + n["dkv"], (self.r + self.rd, W)))
             specs += NORMS.build(self.latent_norm_spec).weight_specs(p)
@@ -84,11 +97,19 @@ class LatentAttentionMixer(Mixer):
 
     def bind(self, get) -> None:
         p, n = self.spec.prefix, self._names()
-        q = get(p + n["q"])
+        if self.q_rank:
+            q = get(p + n["dq"])
+            self.w_uq = get(p + n["uq"])
+            self.q_norm = NORMS.build(self.q_norm_spec)
+            self.q_norm.bind(lambda name: get(p + name))
+        else:
+            q = get(p + n["q"])
         if self.shared:
             self.w_in = q
         else:
-            self.w_in = torch.cat([q, get(p + n["dkv"])], dim=0).contiguous()
+            # with a query latent the two down-projections stay apart: the key part is written where the prep kernel reads it
+            self.w_dkv = get(p + n["dkv"]) if self.q_rank else None
+            self.w_in = q if self.q_rank else torch.cat([q, get(p + n["dkv"])], dim=0).contiguous()
             norm = NORMS.build(self.latent_norm_spec)
             norm.bind(lambda name: get(p + name))
             self.latent_w = norm.weight
@@ -135,8 +156,23 @@ class LatentAttentionMixer(Mixer):
         view = self._view(cache)
         group, index = cache
         decode = lay.all_single
-        proj = ctx.empty((T, self.w_in.shape[0]), torch.float32)
-        linear.matmul(h, self.w_in, proj, linear.EPI_F32, ctx)
+        if self.q_rank:
+            # the query latent and its norm, the queries into the row's first columns, the latent and key part behind them
+            cq_raw = ctx.empty((T, self.q_rank), torch.float32)
+            linear.matmul(h, self.w_in, cq_raw, linear.EPI_F32, ctx)
+            cq = self.q_norm.forward(cq_raw, ctx)
+            nq, tail = H * (dn + rd), 0 if self.shared else r + rd
+            qcols = -(-nq // 4) * 4                            # the key part starts on a 16-byte border
+            proj = ctx.empty((T, qcols + -(-tail // 4) * 4), torch.float32)
+            linear.matmul(cq, self.w_uq, proj[:, :nq], linear.EPI_F32, ctx)
+            kv_in = None
+            if tail:
+                kv_in = proj[:, qcols:qcols + tail]
+                linear.matmul(h, self.w_dkv, kv_in, linear.EPI_F32, ctx)
+        else:
+            proj = ctx.empty((T, self.w_in.shape[0]), torch.float32)
+            linear.matmul(h, self.w_in, proj, linear.EPI_F32, ctx)
+            kv_in = None
         # Whole prompts in bfloat16 with heads of the sizes the tensor-core kernel is built for: keys and values are
         # expanded per head by one product (k_h = U_k,h c, v_h = U_v,h c) and scored as they are; no move into the latent space.
         expanded = self._split_args(ctx, None, None, None, None) is not None
@@ -154,6 +190,8 @@ class LatentAttentionMixer(Mixer):
         append_now = not self.shared and (decode or view.ring_rows == 0 or lay.all_fresh)
         la = K.LatentArgs()
         la.inp, la.in_stride = proj.data_ptr(), proj.stride(0)
+        if kv_in is not None:
+            la.kv_in = kv_in.data_ptr()
         if expanded:
             la.q_full, la.qf_stride = q_full.data_ptr(), q_full.stride(0)
         else:

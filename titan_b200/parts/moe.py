@@ -15,6 +15,10 @@ Options of the spec beyond experts, top and the shared expert:
   tensor, ``correction``), and only among the ``keep`` groups (``groups`` equal groups of neighbouring experts) whose
   best such score is largest (the others count as minus infinity); the weights are the chosen experts' s divided by
   their sum (+ 1e-20).  The default (``"top_softmax"``) takes the top logits and the softmax over them alone.
+* ``routing = "sigmoid_all"``: scores s = sigmoid(z), each output on its own; the rest as above, with two more options:
+  ``group_best`` = n (a group's score is the sum of its n largest s + correction; 1: its best one) and ``renormalize`` =
+  False (the weights are the chosen experts' s as they are).
+* ``shared_gate`` = False: the shared expert's output is added as it is (no sigmoid gate, no tensor for one).
 * ``identity = n``: the last n router outputs are experts without matrices whose output is the input row itself (times
   the weight); they take part in the scores, the groups and the choice like any other.
 * ``activation``: ``silu`` (silu(g) u) or ``swish_clamped`` with ``limit``: g' = min(g, limit), u' = clamp(u, -limit, limit),
@@ -48,8 +52,13 @@ class MixtureOfExperts(FeedForward):
         if s.activation == "swish_clamped" and not self.limit > 0:
             raise ValueError("the clamped gate needs a positive limit")
         self.routing = s.option("routing", "top_softmax")
-        if self.routing not in ("top_softmax", "softmax_all"):
-            raise ValueError(f"routing '{self.routing}' is not known (top_softmax, softmax_all)")
+        if self.routing not in ("top_softmax", "softmax_all", "sigmoid_all"):
+            raise ValueError(f"routing '{self.routing}' is not known (top_softmax, softmax_all, sigmoid_all)")
+        self.scored = self.routing in ("softmax_all", "sigmoid_all")            # scores over all outputs, correction, groups
+        self.group_best, self.renormalize = int(s.option("group_best", 1)), bool(s.option("renormalize", True))
+        self.shared_gate = bool(s.option("shared_gate", True))
+        if self.group_best < 1 or (not self.scored and (self.group_best != 1 or not self.renormalize)):
+            raise ValueError("group_best and renormalize are options of the routings that score all outputs")
         self.identity = int(s.option("identity", 0))
         self.groups, self.keep = int(s.option("groups", 1)), int(s.option("keep", 1))
         self.E, self.top, self.F = int(s.option("experts", 0)), int(s.option("top", 0)), s.intermediate_size
@@ -83,12 +92,14 @@ class MixtureOfExperts(FeedForward):
             q = p + n["expert"].format(e)
             specs += [WeightSpec(q + n["gate"], (self.F, H)), WeightSpec(q + n["up"], (self.F, H)), WeightSpec(q + n["down"], (H, self.F))]
         specs.append(WeightSpec(p + n["router"], (self.n_all, H)))
-        if self.routing == "softmax_all":
+        if self.scored:
             specs.append(WeightSpec(p + n["correction"], (self.n_all,), "vector", ("normal", 0.02)))
         if self.shared_F:
             q = p + n["shared"]
             specs += [WeightSpec(q + n["gate"], (self.shared_F, H)), WeightSpec(q + n["up"], (self.shared_F, H)),
-                      WeightSpec(q + n["down"], (H, self.shared_F)), WeightSpec(p + n["shared_gate"], (1, H))]
+                      WeightSpec(q + n["down"], (H, self.shared_F))]
+            if self.shared_gate:
+                specs.append(WeightSpec(p + n["shared_gate"], (1, H)))
         return specs
 
     def bind(self, get) -> None:
@@ -103,11 +114,11 @@ class MixtureOfExperts(FeedForward):
             self.w_gate_up[e, 1::2] = get(q + n["up"])
             self.w_down[e] = get(q + n["down"])
         router = get(p + n["router"])
-        if self.routing == "softmax_all":
+        if self.scored:
             self.correction = get(p + n["correction"])
         if self.shared_F:
             q = p + n["shared"]
-            self.w_router = torch.cat([router, get(p + n["shared_gate"])], dim=0).contiguous()
+            self.w_router = torch.cat([router, get(p + n["shared_gate"])], dim=0).contiguous() if self.shared_gate else router
             self.ws_gate_up = torch.stack([get(q + n["gate"]), get(q + n["up"])], dim=1).reshape(2 * self.shared_F, H).contiguous()
             self.ws_down = get(q + n["down"])
         else:
@@ -118,14 +129,17 @@ class MixtureOfExperts(FeedForward):
         P = T * top
         f32, i32 = torch.float32, torch.int32
         ids, wts = ctx.empty((T, top), i32), ctx.empty((T, top), f32)
-        gate = ctx.empty((T,), f32) if self.shared_F else None
+        gate = ctx.empty((T,), f32) if self.shared_F and self.shared_gate else None
         n_logits = self.w_router.shape[0]
         z = ctx.empty((T, -(-n_logits // 4) * 4), f32)[:, :n_logits]       # rows of whole 16 bytes: the tensor-core product's output rule
         linear.matmul(h, self.w_router, z, linear.EPI_F32, ctx)
-        if self.routing == "softmax_all":
+        if self.routing == "softmax_all" and self.group_best == 1 and self.renormalize:
             K.moe_route_all(z, top, self.correction, self.groups, self.keep, ids, wts, ctx.stream)
+        elif self.scored:
+            K.moe_route_scored(z, top, self.correction, self.groups, self.keep, ids, wts, ctx.stream,
+                               sigmoid=self.routing == "sigmoid_all", group_best=self.group_best, renorm=self.renormalize)
         else:
-            K.moe_route(z, E, top, bool(self.shared_F), ids, wts, gate, ctx.stream)
+            K.moe_route(z, E, top, gate is not None, ids, wts, gate, ctx.stream)
         shared_y = None
         if self.shared_F:
             act_s = ctx.empty((T, self.shared_F))

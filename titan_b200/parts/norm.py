@@ -1,5 +1,7 @@
 """RMSNorm: y = x / sqrt(mean(x^2) + eps) * (offset + w), float32 inside; offset 0 uses the weight as stored,
 offset 1 is for checkpoints that store the weight's deviation from one (``NormSpec.weight_offset``).
+With ``NormSpec.groups`` = n > 1 the row is cut into n equal runs and every run is divided by its own root mean square;
+the weight still spans the whole row.
 
 berniehans/titan: engine/engine-core/src/forward_cpu.rs:189-200 (eps inside the
 sqrt; no ``1 + w``); kernel engine/engine-cuda/kernels/norm_rope.cu:37-80.
@@ -38,6 +40,9 @@ def rows_of(h):
 class RMSNorm(Norm):
     def __init__(self, spec):
         self.spec = spec
+        self.groups = int(getattr(spec, "groups", 1))
+        if self.groups < 1 or spec.size % self.groups:
+            raise ValueError(f"{self.groups} groups do not divide a norm over {spec.size} elements")
         self.weight: Optional[torch.Tensor] = None
 
     def weight_specs(self, prefix: str) -> List[WeightSpec]:
@@ -50,13 +55,18 @@ class RMSNorm(Norm):
         self.weight = w if self.spec.weight_offset == 0.0 else (w.float() + float(self.spec.weight_offset)).contiguous()
 
     def deferred(self, x: torch.Tensor, ctx) -> DeferredNorm:
+        if self.groups != 1:
+            raise ValueError("a norm in groups cannot be folded into a matrix product")
         return DeferredNorm(self, x, ctx)
 
     def forward(self, x: torch.Tensor, ctx, rows: Optional[torch.Tensor] = None, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
         """``out_dtype``: the dtype of the normed rows where it is not the compute dtype (float32 for a norm inside the residual stream)."""
         n = x.shape[0] if rows is None else rows.numel()
         y = ctx.empty((n, self.spec.size), out_dtype)
-        K.rmsnorm(x, self.weight, y, self.spec.eps, ctx.stream, rows)
+        if self.groups > 1:
+            K.group_rmsnorm(x, self.weight, y, self.groups, self.spec.eps, ctx.stream, rows)
+        else:
+            K.rmsnorm(x, self.weight, y, self.spec.eps, ctx.stream, rows)
         return y
 
 
