@@ -53,6 +53,8 @@ def distance_bucket(n, rows, far):
     """Row of the distance table for a distance n >= 0: one row a distance below rows/2, then logarithmic steps that reach
     the last row at ``far``."""
     half = rows // 2
+    if rows < 2:
+        return 0
     if n < half:
         return n
     return min(rows - 1, half + int(math.floor(math.log(n / half) / math.log(far / half) * (rows - half))))
@@ -70,11 +72,12 @@ def softmax_attention(h, P, pre, m, eps):
     k = unit_rms(k, eps) * P[pre + "k.norm"]
     q, k, v = q.reshape(T, H, d), k.reshape(T, G, d), v.reshape(T, G, dv)
     rel, talk = P[pre + "rel"], P[pre + "talk"]
-    rows, cap = rel.shape[0], float(m["softcap"])
+    rows, cap = rel.shape[0], m.get("softcap")
     s = np.empty((H, T, T))
     for hd in range(H):
         s[hd] = (q[:, hd] @ k[:, hd // (H // G)].T) * m["scale"]
-    s = cap * np.tanh(s / cap)
+    if cap is not None:
+        s = cap * np.tanh(s / cap)
     for i in range(T):
         for j in range(i + 1):
             s[:, i, j] += rel[distance_bucket(i - j, rows, m["bias_max"])]
