@@ -623,6 +623,23 @@ def zadinex_config(width, layers, heads, experts, top, ff, shared_ff, window=Non
     return {"architecture": "Zadinex", "vocab": vocab, "width": width, "norm": {"eps": 1e-6}, "layers": out}
 
 
+def desalorn_config(width, layers, heads, experts, top, ff, shared_ff, window, vocab=32768):
+    """A Desalorn model of the same sizes: latent attention over a window (heads of 128 + 64, queries through a latent of 768),
+    retention (heads of 128), attention with capped, biased and blended scores (heads of 128, a quarter as many kv heads), retention;
+    one norm in four groups feeds a layer's mixer and its mixture of experts (four groups of experts, two open, a shared expert)."""
+    moe = {"kind": "moe", "expert": {"ff": ff}, "router": {"experts": experts, "top": top, "groups": {"count": 4, "keep": 2}}, "shared": {"ff": shared_ff}}
+    decay = [1.0 - 2.0 ** (-5 - 3 * h / max(1, heads - 1)) for h in range(heads)]
+    kinds = {"latent_attention": {"heads": heads, "dim": 128, "rot_dim": 64, "vdim": 128, "kv_rank": 512, "q_rank": 768, "mask": {"size": window},
+                                  "rot": {"base": 10000.0, "dims": 64}, "scale": 1.0 / (192 ** 0.5)},
+             "retention": {"heads": heads, "dim": 128, "vdim": 128, "decay": decay, "rot": {"base": 10000.0, "dims": 128}},
+             "attention": {"heads": heads, "kv_heads": max(1, heads // 4), "dim": 128, "vdim": 128, "scale": 128 ** -0.5, "softcap": 50.0,
+                           "bias_max": 128, "bias_rows": 32}}
+    order = ["latent_attention", "retention", "attention", "retention"]
+    out = [{"type": order[i % 4], "mixer": kinds[order[i % 4]], "mlp": moe} for i in range(layers)]
+    return {"architecture": "Desalorn", "vocab": vocab, "width": width, "norm": {"eps": 1e-5, "groups": 4}, "residual_mult": 0.3,
+            "embedding": {"scale": 1.0}, "layers": out}
+
+
 def qwen3_like(width, layers, heads, ffn, vocab=32768):
     """The dense model of equal size: the same width, depth and heads, and a feed-forward as wide as what one token uses
     of the mixture (its chosen experts and the shared one)."""
@@ -639,7 +656,8 @@ def launcher_times(engine, torch, K, entries):
                          "attn_prefill_mma", "attn_prefill_tc", "attn_prefill_split", "moe_gather", "latent_prep", "latent_append", "lightning_scan", "lightning_chunks",
                          "gated_rmsnorm", "moe_route", "token_gate_rows", "moe_plan", "moe_grouped", "moe_rows", "moe_combine", "moe_experts_tc",
                          "dyt", "scale_add", "wkv", "moe_route_all", "hyper", "polynorm", "gate_rows", "head_norm_gate", "delta_prep",
-                         "recurrent_scan") if hasattr(K, n)]
+                         "recurrent_scan", "group_rmsnorm", "residual_group_norm", "qkv_whole_norm", "attn_mixed_prefill", "attn_mixed_decode",
+                         "rotary_rows", "moe_route_scored") if hasattr(K, n)]
     events, originals = [], {n: getattr(K, n) for n in names}
 
     def wrap(name, f):
@@ -670,10 +688,11 @@ def launcher_times(engine, torch, K, entries):
 
 
 def run_design(args):
-    """``--design tefezen | zadinex | vuvosun``: prompt and decode throughput of that design at sizes that resemble a served
-    model's layers (random weights), beside the Qwen3 dense model of equal size and beside the closest design (for zadinex:
+    """``--design tefezen | zadinex | vuvosun | desalorn``: prompt and decode throughput of that design at sizes that resemble a
+    served model's layers (random weights), beside the Qwen3 dense model of equal size and beside the closest design (for zadinex:
     Tefezen, windowed attention, a recurrence, mixtures of experts; for vuvosun: Zadinex with dense feed-forwards, attention
-    with a sink and a recurrence over a matrix state), and where a step's time goes by launcher."""
+    with a sink and a recurrence over a matrix state; for desalorn: Tefezen, latent attention over a window, decayed linear
+    attention, mixtures of experts with a shared one), and where a step's time goes by launcher."""
     import torch
 
     from titan_b200 import Engine, StepEntry, kernels as K
@@ -687,9 +706,12 @@ def run_design(args):
     results = []
     for sz in sizes:
         row = {"size": sz}
-        beside = {"tefezen": ("qwen3",), "zadinex": ("tefezen", "qwen3"), "vuvosun": ("zadinex_dense", "qwen3")}[args.design]
+        beside = {"tefezen": ("qwen3",), "zadinex": ("tefezen", "qwen3"), "vuvosun": ("zadinex_dense", "qwen3"),
+                  "desalorn": ("tefezen", "qwen3")}[args.design]
         for which in (args.design,) + beside:
-            if which == "vuvosun":
+            if which == "desalorn":
+                cfg = desalorn_config(**sz)
+            elif which == "vuvosun":
                 cfg = vuvosun_config(**sz)
             elif which == "zadinex_dense":
                 cfg = zadinex_config(**sz, dense=True)
@@ -744,7 +766,7 @@ def main():
     ap.add_argument("--micro", action="store_true", help="time the layer's kernels alone (CUDA events) and exit; text lines, not the JSON line")
     ap.add_argument("--timeline", type=int, default=0, metavar="BATCH", help="when the CTAs of one captured decode step's kernels start, wait and end "
                     "(needs TITAN_B200_NVCC_FLAGS=-DTB_TIMELINE); text lines, not the JSON line")
-    ap.add_argument("--design", default=None, choices=["tefezen", "zadinex", "vuvosun"], help="prompt and decode throughput of another design at a few sizes beside "
+    ap.add_argument("--design", default=None, choices=["tefezen", "zadinex", "vuvosun", "desalorn"], help="prompt and decode throughput of another design at a few sizes beside "
                     "the dense model of equal size; one JSON line of its own, the default workload is not run")
     ap.add_argument("--design-size", type=int, default=None, choices=[0, 1], help="with --design: one of its sizes only")
     args = ap.parse_args()
