@@ -192,6 +192,32 @@ def test_attention_alone(dtype, H, G, dim, vdim, cap, rows, far):
             rows_close(got[i], want[i], dtype, f"sequence {i}, portions {sizes}", row_factor=6.0)
 
 
+@pytest.mark.parametrize("dtype", BOTH)
+@pytest.mark.parametrize("H,G,dim,vdim,cap,rows,far", [ATTENTION_SIZES[0], ATTENTION_SIZES[1], ATTENTION_SIZES[4], ATTENTION_SIZES[5]])
+def test_attention_on_the_one_query_prompt_kernel(dtype, H, G, dim, vdim, cap, rows, far):
+    """The prompt kernel that every size falls back to (a block a query, rows read from the cache and the step as they lie),
+    against the plain result: whole prompts and portions."""
+    from titan_b200 import kernels as K
+    from titan_b200.cache import SequenceCache
+    from titan_b200.parts import MIXERS
+    mixer = MIXERS.build(attention_spec(H, G, dim, vdim, 0.4, cap, rows, far))
+    w = attention_weights(mixer, 3, H)
+    bind(mixer, w, DT[dtype])
+    m = attention(H, G, dim, vdim, 0.4, cap, rows, far)
+    lens = [150, 71]
+    xs = inputs(lens, 5)
+    want = [t64(P.softmax_attention(x.numpy(), plain_weights(w, "a."), "", m, 1e-5)) for x in xs]
+    cache = SequenceCache([mixer.cache_need()], 1024, 4, 512, DT[dtype], "cuda", mark_freed=True)
+    K.set_attn_mixed_tile(False)
+    try:
+        for sizes in ([lens], [[60, 33], [50, 2], [2, 2]]):
+            got = drive(mixer_step(mixer, cache), cache, xs, dtype, sizes)
+            for i in range(2):
+                rows_close(got[i], want[i], dtype, f"sequence {i}, portions {sizes}", row_factor=6.0)
+    finally:
+        K.set_attn_mixed_tile(True)
+
+
 LAST = 229
 
 

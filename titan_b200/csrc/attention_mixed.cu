@@ -5,7 +5,10 @@
 //                           its key elements by another, times a weight as wide as the projection; writes the queries, the
 //                           step's own K | V rows and the cache rows; adds the output projection's bias into the rows that
 //                           the output projection will add into.  float32 in, compute dtype out.
-//   tb_attn_mixed_prefill   queries of a ragged step over cache + step rows
+//   tb_attn_mixed_prefill   queries of a ragged step over cache + step rows.  Where the tiles fit shared memory, a block takes
+//                           TILE_Q neighbouring queries of one sequence and stages every round's 32 keys and values of all kv
+//                           heads in shared memory once, for all the heads that read them and for both queries (what bounds the
+//                           one-query kernel is the L2 traffic of every head of every query fetching its own rows)
 //   tb_attn_mixed_decode    one query a sequence over its cached keys, cut into splits (tb_split_keys); partials in the
 //                           layout of tb_attn_merge, which finishes
 //
@@ -156,15 +159,32 @@ __device__ __forceinline__ void attend_mixed(Running& st, const float* qs, float
         st.m = m_new;
 #pragma unroll
         for (int j = 0; j < MIX_MAXE; ++j) st.acc[j] *= alpha;
+        // Values: four keys at a time, all their loads issued before the sums (a key's loads alone would wait out a round
+        // trip to L2 each).  Lanes beyond the range hold p = 0 and the address of the round's first row, so a group of four
+        // needs no tail.
+        const unsigned long long v_first = __shfl_sync(0xffffffffu, (unsigned long long)vp, 0);
+        const unsigned long long v_mine = valid ? (unsigned long long)vp : v_first;
         const int n_valid = min(32, hi - base);
-        for (int kk = 0; kk < n_valid; ++kk) {
-            const float pk = __shfl_sync(0xffffffffu, p, kk);
-            const T* v = (const T*)__shfl_sync(0xffffffffu, (unsigned long long)vp, kk);
+        for (int kk = 0; kk < n_valid; kk += 4) {
+            float pk[4];
+            const T* v[4];
 #pragma unroll
-            for (int j = 0; j < MIX_MAXE; ++j) {
-                const int d = lane + 32 * j;
-                if (d < hdv) st.acc[j] = fmaf(pk, ldf(v + d), st.acc[j]);
+            for (int u = 0; u < 4; ++u) {
+                pk[u] = __shfl_sync(0xffffffffu, p, kk + u);
+                v[u] = (const T*)__shfl_sync(0xffffffffu, v_mine, kk + u);
             }
+            float x[4][MIX_MAXE];
+#pragma unroll
+            for (int u = 0; u < 4; ++u)
+#pragma unroll
+                for (int j = 0; j < MIX_MAXE; ++j) {
+                    const int d = lane + 32 * j;
+                    x[u][j] = d < hdv ? ldf(v[u] + d) : 0.f;
+                }
+#pragma unroll
+            for (int u = 0; u < 4; ++u)
+#pragma unroll
+                for (int j = 0; j < MIX_MAXE; ++j) st.acc[j] = fmaf(pk[u], x[u][j], st.acc[j]);
         }
     }
 }
@@ -245,6 +265,178 @@ __global__ void __launch_bounds__(1024) attn_mixed_decode_kernel(AttnArgs a) {
     if (lane == 0) { part[hdv] = st.m; part[hdv + 1] = st.l; }
 }
 
+template <typename T> __device__ __forceinline__ float2 pair2(const T* p);
+template <> __device__ __forceinline__ float2 pair2<float>(const float* p) { return *reinterpret_cast<const float2*>(p); }
+template <> __device__ __forceinline__ float2 pair2<__nv_bfloat16>(const __nv_bfloat16* p) {
+    const uint32_t w = *reinterpret_cast<const uint32_t*>(p);
+    return make_float2(__uint_as_float(w << 16), __uint_as_float(w & 0xffff0000u));
+}
+template <typename T> __device__ __forceinline__ void copy8(T* dst, const T* src);
+template <> __device__ __forceinline__ void copy8<float>(float* dst, const float* src) {
+    reinterpret_cast<float4*>(dst)[0] = reinterpret_cast<const float4*>(src)[0];
+    reinterpret_cast<float4*>(dst)[1] = reinterpret_cast<const float4*>(src)[1];
+}
+template <> __device__ __forceinline__ void copy8<__nv_bfloat16>(__nv_bfloat16* dst, const __nv_bfloat16* src) {
+    *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<const uint4*>(src);
+}
+template <typename T> __device__ __forceinline__ void zero8(T* dst);
+template <> __device__ __forceinline__ void zero8<float>(float* dst) {
+    reinterpret_cast<float4*>(dst)[0] = make_float4(0.f, 0.f, 0.f, 0.f);
+    reinterpret_cast<float4*>(dst)[1] = make_float4(0.f, 0.f, 0.f, 0.f);
+}
+template <> __device__ __forceinline__ void zero8<__nv_bfloat16>(__nv_bfloat16* dst) { *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0); }
+
+#define TILE_Q 2            // queries a block of the tiled kernel takes
+#define TILE_MAXJ 4         // a lane holds value dims 2 * lane + 64 j and the next one: rows of up to 256
+
+// Shared memory of the tiled kernel, in this order: TILE_Q * nh * hd query floats; TILE_Q * 2 * nh * 32 scores; then the
+// K tile and the V tile, each nkv * 32 rows of hd + 8 elements of T (the 8 spare elements keep a lane's 16-byte reads of
+// its own row off its neighbours' banks).
+template <typename T>
+size_t tile_smem(const AttnArgs& a) {
+    return ((size_t)TILE_Q * a.nh * a.hd + (size_t)TILE_Q * 2 * a.nh * 32) * sizeof(float) + 2 * (size_t)a.nkv * 32 * (a.hd + 8) * sizeof(T);
+}
+
+// grid (ceil(max_new / TILE_Q), B); block of nh warps.  Block (i, b) takes queries i * TILE_Q .. of sequence b.
+template <typename T>
+__global__ void __launch_bounds__(1024) attn_mixed_prefill_tile_kernel(AttnArgs a) {
+    pdl_launch_dependents();
+    pdl_wait();
+    extern __shared__ __align__(16) float sm[];
+    const int lane = threadIdx.x & 31, h = threadIdx.x >> 5;
+    const int b = blockIdx.y, hd = a.hd, nh = a.nh, nkv = a.nkv, row = hd + 8;
+    const int hdv = a.hd_v > 0 ? a.hd_v : a.hd;
+    const int t0 = a.batch.q_start[b] + blockIdx.x * TILE_Q, t_end = a.batch.q_start[b + 1];
+    if (t0 >= t_end) return;
+    const int nq = min(TILE_Q, t_end - t0);
+    float* qs = sm;
+    float* raw = qs + TILE_Q * nh * hd;
+    T* kt = reinterpret_cast<T*>(raw + TILE_Q * 2 * nh * 32);
+    T* vt = kt + (size_t)nkv * 32 * row;
+    for (int e = threadIdx.x; e < TILE_Q * nh * hd; e += blockDim.x) {
+        const int q = e / (nh * hd), i = e % (nh * hd);
+        qs[e] = q < nq ? ldf((const T*)a.q + (size_t)(t0 + q) * a.q_stride + i) : 0.f;
+    }
+    const float mix_w = (a.head_mix && lane < nh) ? a.head_mix[h * nh + lane] : 0.f;
+    const int slot = a.batch.slot_of_seq[b];
+    const int pos0 = a.batch.pos_of[t0], pos_last = pos0 + nq - 1;
+    const int first_new = a.kv_new ? a.batch.start_pos[b] : 0x7fffffff, first_new_row = a.batch.q_start[b];
+    const int lo = a.window > 0 ? max(0, pos0 - a.window + 1) : 0, hi = pos_last + 1;
+    const int kh = h / (nh / nkv);
+    const T* knew = (const T*)a.kv_new;
+    const T* cache = (const T*)a.cache.storage;
+    const size_t vhalf = cache ? kv_half_elems(a.cache) : 0;
+    const int chunks = hd >> 3;
+    float m_run[TILE_Q], l_run[TILE_Q], acc[TILE_Q][2 * TILE_MAXJ];
+#pragma unroll
+    for (int q = 0; q < TILE_Q; ++q) {
+        m_run[q] = -FLT_MAX; l_run[q] = 0.f;
+#pragma unroll
+        for (int j = 0; j < 2 * TILE_MAXJ; ++j) acc[q][j] = 0.f;
+    }
+    int round = 0;
+    for (int base = lo; base < hi; base += 32, ++round) {
+        __syncthreads();                                    // the tiles of the round before have been read (and the queries are in place)
+        for (int c = threadIdx.x; c < 2 * nkv * 32 * chunks; c += blockDim.x) {
+            const int part = c % chunks, r = (c / chunks) % 32, g = (c / (chunks * 32)) % nkv, is_v = c / (chunks * 32 * nkv);
+            const int kpos = base + r;
+            T* dst = (is_v ? vt : kt) + ((size_t)g * 32 + r) * row + part * 8;
+            if (kpos >= hi) { zero8<T>(dst); continue; }
+            const T* src = kpos >= first_new
+                ? knew + (size_t)(first_new_row + kpos - first_new) * a.kv_stride + (is_v ? nkv * hd : 0) + g * hd
+                : cache + (is_v ? vhalf : 0) + kv_row_offset(a.cache, slot, kpos, g);
+            copy8<T>(dst, src + part * 8);
+        }
+        __syncthreads();
+        const int kpos = base + lane;
+        float s[TILE_Q];
+#pragma unroll
+        for (int q = 0; q < TILE_Q; ++q) s[q] = 0.f;
+        {
+            const T* kp = kt + ((size_t)kh * 32 + lane) * row;
+            for (int e = 0; e < hd; e += 8) {
+                float kv[8];
+                row8<T>(kp + e, kv);
+#pragma unroll
+                for (int q = 0; q < TILE_Q; ++q) {
+                    const float* qv = qs + (q * nh + h) * hd + e;
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) s[q] = fmaf(qv[i], kv[i], s[q]);
+                }
+            }
+        }
+        bool seen[TILE_Q];
+#pragma unroll
+        for (int q = 0; q < TILE_Q; ++q) {
+            const int qpos = pos0 + q;
+            seen[q] = q < nq && kpos <= qpos && (a.window <= 0 || kpos > qpos - a.window);
+            float v = 0.f;
+            if (seen[q]) {
+                v = s[q] * a.scale;
+                if (a.softcap > 0.f) v = a.softcap * tanhf(v / a.softcap);
+                if (a.rel_bias) v += a.rel_bias[(size_t)min(qpos - kpos, a.rel_far) * nh + h];
+            }
+            s[q] = v;
+        }
+        if (a.head_mix) {
+            float* buf = raw + (round & 1) * TILE_Q * nh * 32;
+#pragma unroll
+            for (int q = 0; q < TILE_Q; ++q) buf[(q * nh + h) * 32 + lane] = s[q];
+            __syncthreads();
+#pragma unroll
+            for (int q = 0; q < TILE_Q; ++q) s[q] = 0.f;
+            for (int g = 0; g < nh; ++g) {
+                const float w = __shfl_sync(0xffffffffu, mix_w, g);
+#pragma unroll
+                for (int q = 0; q < TILE_Q; ++q) s[q] = fmaf(w, buf[(q * nh + g) * 32 + lane], s[q]);
+            }
+        }
+        float p[TILE_Q];
+#pragma unroll
+        for (int q = 0; q < TILE_Q; ++q) {
+            const float sv = seen[q] ? s[q] : -FLT_MAX;
+            const float m_new = fmaxf(m_run[q], warp_max(sv));
+            const float alpha = expf(m_run[q] - m_new);
+            p[q] = seen[q] ? expf(sv - m_new) : 0.f;
+            l_run[q] = l_run[q] * alpha + warp_sum(p[q]);
+            m_run[q] = m_new;
+#pragma unroll
+            for (int j = 0; j < 2 * TILE_MAXJ; ++j) acc[q][j] *= alpha;
+        }
+        const T* vbase = vt + (size_t)kh * 32 * row + 2 * lane;
+        const int n_valid = min(32, hi - base);
+        for (int kk = 0; kk < n_valid; ++kk) {
+            float pk[TILE_Q];
+#pragma unroll
+            for (int q = 0; q < TILE_Q; ++q) pk[q] = __shfl_sync(0xffffffffu, p[q], kk);
+            const T* v = vbase + (size_t)kk * row;
+#pragma unroll
+            for (int j = 0; j < TILE_MAXJ; ++j) {
+                if (2 * lane + 64 * j < hdv) {
+                    const float2 x = pair2<T>(v + 64 * j);
+#pragma unroll
+                    for (int q = 0; q < TILE_Q; ++q) {
+                        acc[q][2 * j] = fmaf(pk[q], x.x, acc[q][2 * j]);
+                        acc[q][2 * j + 1] = fmaf(pk[q], x.y, acc[q][2 * j + 1]);
+                    }
+                }
+            }
+        }
+    }
+#pragma unroll
+    for (int q = 0; q < TILE_Q; ++q) {
+        if (q >= nq) break;
+        float inv = 1.0f / l_run[q];
+        if (a.head_gate) inv *= 1.0f / (1.0f + expf(-a.head_gate[(size_t)(t0 + q) * a.head_gate_stride + h]));
+        T* o = (T*)a.out + (size_t)(t0 + q) * a.out_stride + h * hdv;
+#pragma unroll
+        for (int j = 0; j < TILE_MAXJ; ++j) {
+            const int d = 2 * lane + 64 * j;
+            if (d < hdv) { stf(o + d, acc[q][2 * j] * inv); stf(o + d + 1, acc[q][2 * j + 1] * inv); }
+        }
+    }
+}
+
 int check_mixed(const AttnArgs& a, const char* who) {
     TB_REQUIRE(a.nh > 0 && a.nkv > 0 && a.nh % a.nkv == 0, "%s: %d query heads are not a multiple of %d kv heads", who, a.nh, a.nkv);
     TB_REQUIRE(a.nh <= 32, "%s: %d heads (one warp a head, at most 32)", who, a.nh);
@@ -263,6 +455,9 @@ size_t mixed_smem(const AttnArgs& a) { return ((size_t)a.nh * a.hd + 2 * (size_t
 }  // namespace
 
 extern "C" int tb_attn_merge(const AttnArgs* args, int dtype, cudaStream_t stream);
+
+static int g_mixed_tile = 1;
+extern "C" int tb_set_attn_mixed_tile(int on) { g_mixed_tile = on ? 1 : 0; return 0; }
 
 extern "C" int tb_qkv_whole_norm(const WholeNormArgs* args, int out_dtype, cudaStream_t stream) {
     WholeNormArgs a = *args;
@@ -283,6 +478,26 @@ extern "C" int tb_attn_mixed_prefill(const AttnArgs* args, int dtype, cudaStream
     AttnArgs a = *args;
     if (check_mixed(a, "attn_mixed_prefill")) return 1;
     TB_REQUIRE(a.batch.T > 0 && (a.kv_new || a.cache.storage), "attn_mixed_prefill: no tokens, or neither new keys nor a cache");
+    TB_REQUIRE(dtype == TB_F32 || dtype == TB_BF16, "attn_mixed_prefill: unknown dtype %d", dtype);
+    // The tiled kernel where a round's keys and values of every kv head fit shared memory beside the queries (value rows of an
+    // even width, so that a lane's pair of dims is whole); g_mixed_tile 0 keeps the one-query kernel (tests compare the two).
+    const size_t tsmem = dtype == TB_F32 ? tile_smem<float>(a) : tile_smem<__nv_bfloat16>(a);
+    const int hdv = a.hd_v > 0 ? a.hd_v : a.hd;
+    if (g_mixed_tile && tsmem <= 200 * 1024 && hdv % 2 == 0 && a.batch.max_new > 1 && a.batch.B <= 65535) {
+        static bool configured[2] = {false, false};
+        if (!configured[dtype == TB_BF16]) {
+            const cudaError_t e = dtype == TB_F32
+                ? cudaFuncSetAttribute(attn_mixed_prefill_tile_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024)
+                : cudaFuncSetAttribute(attn_mixed_prefill_tile_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+            TB_REQUIRE(e == cudaSuccess, "attn_mixed_prefill: cannot reserve shared memory: %s", cudaGetErrorString(e));
+            configured[dtype == TB_BF16] = true;
+        }
+        dim3 grid((a.batch.max_new + TILE_Q - 1) / TILE_Q, a.batch.B);
+        if (dtype == TB_F32) tb_launch(attn_mixed_prefill_tile_kernel<float>, grid, a.nh * 32, tsmem, stream, a);
+        else tb_launch(attn_mixed_prefill_tile_kernel<__nv_bfloat16>, grid, a.nh * 32, tsmem, stream, a);
+        TB_CHECK_LAUNCH("attn_mixed_prefill");
+        return 0;
+    }
     const size_t smem = mixed_smem(a);
     TB_REQUIRE(smem <= 48 * 1024, "attn_mixed_prefill: %d heads of %d need %zu bytes of shared memory (at most 48 KB)", a.nh, a.hd, smem);
     if (dtype == TB_F32) tb_launch(attn_mixed_prefill_kernel<float>, a.batch.T, a.nh * 32, smem, stream, a);

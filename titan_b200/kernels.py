@@ -205,6 +205,7 @@ def lib():
         l.tb_qkv_whole_norm.argtypes = [POINTER(WholeNormArgs), c_int, c_void_p]
         l.tb_attn_mixed_prefill.argtypes = [POINTER(AttnArgs), c_int, c_void_p]
         l.tb_attn_mixed_decode.argtypes = [POINTER(AttnArgs), c_int, c_void_p]
+        l.tb_set_attn_mixed_tile.argtypes = [c_int]
         l.tb_rotary_rows.argtypes = [c_void_p, c_int, c_void_p, c_int, c_int, c_int, POINTER(RotaryArgs), c_int, c_float, c_void_p]
         l.tb_gemm_simt_batched.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
                                            c_longlong, c_longlong, c_longlong, c_void_p]
@@ -539,6 +540,12 @@ def qkv_whole_norm(args: "WholeNormArgs", out_dtype: torch.dtype, stream: int) -
 
 def attn_mixed_prefill(args: AttnArgs, dtype: torch.dtype, stream: int) -> None:
     _check(lib().tb_attn_mixed_prefill(byref(args), dtype_code(dtype), stream))
+
+
+def set_attn_mixed_tile(on: bool) -> None:
+    """Prompt attention with blended heads: the kernel that stages a round's keys and values in shared memory for two queries
+    and all heads (default), or (off) the one-query kernel that every size falls back to; the tests compare the two."""
+    lib().tb_set_attn_mixed_tile(int(on))
 
 
 def attn_mixed_decode(args: AttnArgs, dtype: torch.dtype, stream: int) -> None:

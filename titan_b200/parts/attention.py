@@ -367,7 +367,10 @@ class AttentionMixer(Mixer):
         if self.head_gate_name:
             aa.head_gate, aa.head_gate_stride = proj.data_ptr() + (Q + 2 * KV) * 4, width
         if decode:
-            chunk, splits = decode_split(lay, view.kv_heads, ctx.options, False)
+            # a block takes all heads of one split of one sequence: splits of 32 keys (one round) while the sequences are few,
+            # longer ones as they grow in number; by the batch size alone, so that eager and captured steps cut alike
+            chunk = int(ctx.options.get("mixed_chunk", 32 if lay.B <= 4 else (64 if lay.B <= 16 else (128 if lay.B <= 64 else 256))))
+            chunk, splits = decode_split(lay, view.kv_heads, dict(ctx.options, attn_chunk=chunk), False)
             need = lay.B * s.num_heads * splits * (hd + 2)
             scratch = ctx.scratch.get("attn_partials")
             if scratch is None or scratch.numel() < need:
