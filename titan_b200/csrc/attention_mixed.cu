@@ -271,14 +271,17 @@ template <> __device__ __forceinline__ float2 pair2<__nv_bfloat16>(const __nv_bf
     const uint32_t w = *reinterpret_cast<const uint32_t*>(p);
     return make_float2(__uint_as_float(w << 16), __uint_as_float(w & 0xffff0000u));
 }
-template <typename T> __device__ __forceinline__ void copy8(T* dst, const T* src);
-template <> __device__ __forceinline__ void copy8<float>(float* dst, const float* src) {
-    reinterpret_cast<float4*>(dst)[0] = reinterpret_cast<const float4*>(src)[0];
-    reinterpret_cast<float4*>(dst)[1] = reinterpret_cast<const float4*>(src)[1];
-}
-template <> __device__ __forceinline__ void copy8<__nv_bfloat16>(__nv_bfloat16* dst, const __nv_bfloat16* src) {
-    *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<const uint4*>(src);
-}
+template <typename T> struct Chunk8;
+template <> struct Chunk8<float> {
+    float4 a, b;
+    __device__ __forceinline__ void load(const float* p) { a = reinterpret_cast<const float4*>(p)[0]; b = reinterpret_cast<const float4*>(p)[1]; }
+    __device__ __forceinline__ void store(float* p) const { reinterpret_cast<float4*>(p)[0] = a; reinterpret_cast<float4*>(p)[1] = b; }
+};
+template <> struct Chunk8<__nv_bfloat16> {
+    uint4 a;
+    __device__ __forceinline__ void load(const __nv_bfloat16* p) { a = *reinterpret_cast<const uint4*>(p); }
+    __device__ __forceinline__ void store(__nv_bfloat16* p) const { *reinterpret_cast<uint4*>(p) = a; }
+};
 template <typename T> __device__ __forceinline__ void zero8(T* dst);
 template <> __device__ __forceinline__ void zero8<float>(float* dst) {
     reinterpret_cast<float4*>(dst)[0] = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -291,10 +294,11 @@ template <> __device__ __forceinline__ void zero8<__nv_bfloat16>(__nv_bfloat16* 
 
 // Shared memory of the tiled kernel, in this order: TILE_Q * nh * hd query floats; TILE_Q * 2 * nh * 32 scores; then the
 // K tile and the V tile, each nkv * 32 rows of hd + 8 elements of T (the 8 spare elements keep a lane's 16-byte reads of
-// its own row off its neighbours' banks).
+// its own row off its neighbours' banks); then one address a row of the tiles.
 template <typename T>
 size_t tile_smem(const AttnArgs& a) {
-    return ((size_t)TILE_Q * a.nh * a.hd + (size_t)TILE_Q * 2 * a.nh * 32) * sizeof(float) + 2 * (size_t)a.nkv * 32 * (a.hd + 8) * sizeof(T);
+    return ((size_t)TILE_Q * a.nh * a.hd + (size_t)TILE_Q * 2 * a.nh * 32) * sizeof(float) + 2 * (size_t)a.nkv * 32 * (a.hd + 8) * sizeof(T)
+           + 2 * (size_t)a.nkv * 32 * sizeof(void*);           // and where each row of the tiles comes from
 }
 
 // grid (ceil(max_new / TILE_Q), B); block of nh warps.  Block (i, b) takes queries i * TILE_Q .. of sequence b.
@@ -334,20 +338,49 @@ __global__ void __launch_bounds__(1024) attn_mixed_prefill_tile_kernel(AttnArgs 
 #pragma unroll
         for (int j = 0; j < 2 * TILE_MAXJ; ++j) acc[q][j] = 0.f;
     }
+    // Row id (v * nkv + g) * 32 + r is key base + r of kv head g, in the K tile (v = 0) or the V tile (v = 1); src_of[id] is where
+    // its hd elements lie (in the step's own rows or in the cache's page), null past the range.
+    const int n_rows = 2 * nkv * 32;
+    const T** src_of = reinterpret_cast<const T**>(vt + (size_t)nkv * 32 * row);
+    const int cshift = (chunks & (chunks - 1)) == 0 ? __ffs(chunks) - 1 : -1;
+    auto locate_rows = [&](int base) {
+        for (int id = threadIdx.x; id < n_rows; id += blockDim.x) {
+            const int r = id & 31, gv = id >> 5, is_v = gv >= nkv, g = gv - is_v * nkv, kpos = base + r;
+            const T* src = nullptr;
+            if (kpos < hi)
+                src = kpos >= first_new
+                    ? knew + (size_t)(first_new_row + kpos - first_new) * a.kv_stride + (is_v ? nkv * hd : 0) + g * hd
+                    : cache + (is_v ? vhalf : 0) + kv_row_offset(a.cache, slot, kpos, g);
+            src_of[id] = src;
+        }
+    };
+    locate_rows(lo);
     int round = 0;
     for (int base = lo; base < hi; base += 32, ++round) {
-        __syncthreads();                                    // the tiles of the round before have been read (and the queries are in place)
-        for (int c = threadIdx.x; c < 2 * nkv * 32 * chunks; c += blockDim.x) {
-            const int part = c % chunks, r = (c / chunks) % 32, g = (c / (chunks * 32)) % nkv, is_v = c / (chunks * 32 * nkv);
-            const int kpos = base + r;
-            T* dst = (is_v ? vt : kt) + ((size_t)g * 32 + r) * row + part * 8;
-            if (kpos >= hi) { zero8<T>(dst); continue; }
-            const T* src = kpos >= first_new
-                ? knew + (size_t)(first_new_row + kpos - first_new) * a.kv_stride + (is_v ? nkv * hd : 0) + g * hd
-                : cache + (is_v ? vhalf : 0) + kv_row_offset(a.cache, slot, kpos, g);
-            copy8<T>(dst, src + part * 8);
+        __syncthreads();                                    // the tiles of the round before have been read (and the queries and the rows' places are there)
+        // Eight elements a copy, two copies a thread in flight (both loads are issued before the first store).  Where a row comes
+        // from was worked out once a row, by the threads that had the round before's scores to wait for (``src_of``); a row past
+        // the range is stored as zeros.  Copy c is part c % chunks of row c / chunks: a shift where the head's width allows.
+        const int total = n_rows * chunks;
+        for (int c0 = threadIdx.x; c0 < total; c0 += 2 * blockDim.x) {
+            Chunk8<T> held[2];
+            T* dst[2];
+            bool real[2];
+#pragma unroll
+            for (int u = 0; u < 2; ++u) {
+                const int c = min(c0 + u * (int)blockDim.x, total - 1);
+                const int rid = cshift >= 0 ? c >> cshift : c / chunks, part = c - rid * chunks;
+                const T* src = src_of[rid];
+                real[u] = src != nullptr;
+                dst[u] = kt + (size_t)rid * row + part * 8;          // the V tile lies right behind the K tile: row ids run through both
+                held[u].load((real[u] ? src : src_of[0]) + part * 8);
+            }
+#pragma unroll
+            for (int u = 0; u < 2; ++u)
+                if (c0 + u * (int)blockDim.x < total) { if (real[u]) held[u].store(dst[u]); else zero8<T>(dst[u]); }
         }
         __syncthreads();
+        if (base + 32 < hi) locate_rows(base + 32);          // for the next round; nothing reads the list before that round's first barrier
         const int kpos = base + lane;
         float s[TILE_Q];
 #pragma unroll
@@ -484,17 +517,16 @@ extern "C" int tb_attn_mixed_prefill(const AttnArgs* args, int dtype, cudaStream
     const size_t tsmem = dtype == TB_F32 ? tile_smem<float>(a) : tile_smem<__nv_bfloat16>(a);
     const int hdv = a.hd_v > 0 ? a.hd_v : a.hd;
     if (g_mixed_tile && tsmem <= 200 * 1024 && hdv % 2 == 0 && a.batch.max_new > 1 && a.batch.B <= 65535) {
+        void (*kernel)(AttnArgs) = dtype == TB_F32 ? attn_mixed_prefill_tile_kernel<float> : attn_mixed_prefill_tile_kernel<__nv_bfloat16>;
         static bool configured[2] = {false, false};
-        if (!configured[dtype == TB_BF16]) {
-            const cudaError_t e = dtype == TB_F32
-                ? cudaFuncSetAttribute(attn_mixed_prefill_tile_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024)
-                : cudaFuncSetAttribute(attn_mixed_prefill_tile_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+        const int which = dtype == TB_BF16 ? 1 : 0;
+        if (!configured[which]) {
+            const cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
             TB_REQUIRE(e == cudaSuccess, "attn_mixed_prefill: cannot reserve shared memory: %s", cudaGetErrorString(e));
-            configured[dtype == TB_BF16] = true;
+            configured[which] = true;
         }
         dim3 grid((a.batch.max_new + TILE_Q - 1) / TILE_Q, a.batch.B);
-        if (dtype == TB_F32) tb_launch(attn_mixed_prefill_tile_kernel<float>, grid, a.nh * 32, tsmem, stream, a);
-        else tb_launch(attn_mixed_prefill_tile_kernel<__nv_bfloat16>, grid, a.nh * 32, tsmem, stream, a);
+        tb_launch(kernel, grid, a.nh * 32, tsmem, stream, a);
         TB_CHECK_LAUNCH("attn_mixed_prefill");
         return 0;
     }
