@@ -49,9 +49,9 @@ __global__ void __launch_bounds__(256) gate_rows_kernel(const T* x, int ldx, con
     if (i < n) stf(y + t * ldy + i, ldf(x + t * ldx + i) * act_gate(ldf(g + t * ldg + i), act) * scale);
 }
 
-template <typename T>
+template <typename T, typename G>
 __global__ void __launch_bounds__(128) head_norm_gate_kernel(const float* __restrict__ o, int ldo, const float* __restrict__ w, int w_head,
-                                                             const T* __restrict__ g, int ldg, T* __restrict__ y, int ldy,
+                                                             const G* __restrict__ g, int ldg, T* __restrict__ y, int ldy,
                                                              int H, int dv, int act, float scale, float eps) {
     pdl_launch_dependents();
     pdl_wait();
@@ -97,15 +97,26 @@ extern "C" int tb_gate_rows(const void* x, int ldx, const void* g, int ldg, void
     return 0;
 }
 
+extern "C" int tb_head_norm_gate_from(const float* o, int ldo, const float* w, int w_head, const void* g, int ldg, int g_dtype, void* y, int ldy,
+                                      int dtype, int rows, int H, int dv, int act, float scale, float eps, cudaStream_t stream);
+
 extern "C" int tb_head_norm_gate(const float* o, int ldo, const float* w, int w_head, const void* g, int ldg, void* y, int ldy, int dtype,
                                  int rows, int H, int dv, int act, float scale, float eps, cudaStream_t stream) {
+    return tb_head_norm_gate_from(o, ldo, w, w_head, g, ldg, dtype, y, ldy, dtype, rows, H, dv, act, scale, eps, stream);
+}
+
+// The same with the gate's rows in a dtype of their own (g_dtype): float32 gate logits that came out of one product with the
+// recurrence's inputs, beside an output in bfloat16.
+extern "C" int tb_head_norm_gate_from(const float* o, int ldo, const float* w, int w_head, const void* g, int ldg, int g_dtype, void* y, int ldy,
+                                      int dtype, int rows, int H, int dv, int act, float scale, float eps, cudaStream_t stream) {
     TB_REQUIRE(o && w && g && y && rows > 0 && H > 0 && dv > 0, "head_norm_gate: rows of heads are wanted");
     TB_REQUIRE(act == 0 || act == 1, "head_norm_gate: the gate is a sigmoid (0) or silu (1)");
     TB_REQUIRE((H + 3) / 4 <= 65535, "head_norm_gate: too many heads");
     dim3 grid(rows, (H + 3) / 4);
-    if (dtype == TB_F32) tb_launch(head_norm_gate_kernel<float>, grid, dim3(128), 0, stream, o, ldo, w, w_head, (const float*)g, ldg, (float*)y, ldy, H, dv, act, scale, eps);
-    else if (dtype == TB_BF16) tb_launch(head_norm_gate_kernel<__nv_bfloat16>, grid, dim3(128), 0, stream, o, ldo, w, w_head, (const __nv_bfloat16*)g, ldg, (__nv_bfloat16*)y, ldy, H, dv, act, scale, eps);
-    else TB_REQUIRE(false, "head_norm_gate: unknown dtype %d", dtype);
+    if (dtype == TB_F32 && g_dtype == TB_F32) tb_launch(head_norm_gate_kernel<float, float>, grid, dim3(128), 0, stream, o, ldo, w, w_head, (const float*)g, ldg, (float*)y, ldy, H, dv, act, scale, eps);
+    else if (dtype == TB_BF16 && g_dtype == TB_BF16) tb_launch(head_norm_gate_kernel<__nv_bfloat16, __nv_bfloat16>, grid, dim3(128), 0, stream, o, ldo, w, w_head, (const __nv_bfloat16*)g, ldg, (__nv_bfloat16*)y, ldy, H, dv, act, scale, eps);
+    else if (dtype == TB_BF16 && g_dtype == TB_F32) tb_launch(head_norm_gate_kernel<__nv_bfloat16, float>, grid, dim3(128), 0, stream, o, ldo, w, w_head, (const float*)g, ldg, (__nv_bfloat16*)y, ldy, H, dv, act, scale, eps);
+    else TB_REQUIRE(false, "head_norm_gate: unsupported dtypes (output %d, gate %d)", dtype, g_dtype);
     TB_CHECK_LAUNCH("head_norm_gate");
     return 0;
 }

@@ -196,6 +196,8 @@ def lib():
         l.tb_gate_rows.argtypes = [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p]
         l.tb_head_norm_gate.argtypes = [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
                                         c_float, c_float, c_void_p]
+        l.tb_head_norm_gate_from.argtypes = [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
+                                             c_float, c_float, c_void_p]
         l.tb_delta_prep.argtypes = [POINTER(DeltaPrepArgs), c_int, c_void_p]
         l.tb_recurrent_scan.argtypes = [POINTER(ScanArgs), c_int, c_int, c_void_p]
         l.tb_moe_route_all.argtypes = [c_void_p, c_int, c_int, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p]
@@ -465,14 +467,14 @@ def gate_rows(x: torch.Tensor, g: torch.Tensor, y: torch.Tensor, act: int, scale
 def head_norm_gate(o: torch.Tensor, w: torch.Tensor, per_head: bool, g: torch.Tensor, y: torch.Tensor, heads: int, act: int, scale: float,
                    eps: float, stream: int) -> None:
     """Per head of dv = width / heads elements: y = o / sqrt(mean(o^2) + eps) * w * act(g) * scale.  o float32 [T, heads * dv]; w float32, one
-    row of dv for every head or (``per_head``) heads * dv; g and y in the compute dtype (row-strided views allowed)."""
+    row of dv for every head or (``per_head``) heads * dv; y in the compute dtype, g in it or in float32 (row-strided views allowed)."""
     _need_cuda(o, w, g, y)
     dv = o.shape[1] // heads
-    if o.dtype != torch.float32 or w.dtype != torch.float32 or g.dtype != y.dtype or o.stride(1) != 1 or g.stride(1) != 1 or y.stride(1) != 1 \
+    if o.dtype != torch.float32 or w.dtype != torch.float32 or g.dtype not in (y.dtype, torch.float32) or o.stride(1) != 1 or g.stride(1) != 1 or y.stride(1) != 1 \
             or o.shape[1] != heads * dv or w.numel() != (heads * dv if per_head else dv) or g.shape != o.shape or y.shape != o.shape:
         raise KernelError("head_norm_gate: float32 rows of whole heads, a gate and an output of one dtype")
-    _check(lib().tb_head_norm_gate(o.data_ptr(), o.stride(0), w.data_ptr(), dv if per_head else 0, g.data_ptr(), g.stride(0), y.data_ptr(), y.stride(0),
-                                   dtype_code(y.dtype), o.shape[0], heads, dv, int(act), float(scale), float(eps), stream))
+    _check(lib().tb_head_norm_gate_from(o.data_ptr(), o.stride(0), w.data_ptr(), dv if per_head else 0, g.data_ptr(), g.stride(0), dtype_code(g.dtype),
+                                        y.data_ptr(), y.stride(0), dtype_code(y.dtype), o.shape[0], heads, dv, int(act), float(scale), float(eps), stream))
 
 
 def delta_prep(args: "DeltaPrepArgs", dtype: torch.dtype, stream: int) -> None:

@@ -1,6 +1,6 @@
 """Retention as a mixer: linear attention with one fixed decay a head, rotated queries and keys, no softmax and no denominator.
 
-    [q | k | v] = h . [W_q ; W_k ; W_v]^T   (float32 out);   g = h . W_g^T
+    [q | k | v | g] = h . [W_q ; W_k ; W_v ; W_g]^T                  one product, float32 out
     q, k <- rotary(q, k) by position;  k <- k * scale                 heads x dim (``scale`` defaults to dim^-1/2)
     S_t = decay_h S_{t-1} + k_t v_t^T ;  o_t = S_t^T q_t             per head; S float32 [dim, value_dim], zero at the start
     y = concat_h(o_t,h / rms(o_t,h)) * silu(g) ;  out += y . W_o^T   the heads' norms have no weight
@@ -43,7 +43,7 @@ class RetentionMixer(Mixer):
         self.position = POSITIONS.build(s.position)
         if self.position.rotary_dim > self.dk:
             raise ValueError(f"{self.position.rotary_dim} rotated dimensions in a head of {self.dk}")
-        self.w_in = self.w_g = self.w_o = self.decay = self.ones = None
+        self.w_in = self.w_o = self.decay = self.ones = None
 
     def cache_need(self) -> Optional[CacheNeed]:
         return CacheNeed("state", state_shape=(self.H, self.dk, self.dv), state_dtype=torch.float32)
@@ -59,8 +59,8 @@ class RetentionMixer(Mixer):
 
     def bind(self, get) -> None:
         p, n = self.spec.prefix, self._names()
-        self.w_in = torch.cat([get(p + n[role]) for role in ("q", "k", "v")], dim=0).contiguous()
-        self.w_g, self.w_o = get(p + n["g"]), get(p + n["o"])
+        self.w_in = torch.cat([get(p + n[role]) for role in ("q", "k", "v", "g")], dim=0).contiguous()
+        self.w_o = get(p + n["o"])
         dev = self.w_o.device
         self.decay = torch.tensor(self.decay_values, dtype=torch.float32, device=dev)
         self.ones = torch.ones(self.dv, dtype=torch.float32, device=dev)          # the heads' norms have no weight
@@ -73,8 +73,7 @@ class RetentionMixer(Mixer):
             raise TypeError(f"retention keeps its state in a 'state' cache group, not in {type(group).__name__}")
         proj = ctx.empty((T, self.w_in.shape[0]), torch.float32)
         linear.matmul(h, self.w_in, proj, linear.EPI_F32, ctx)
-        gate = ctx.empty((T, H * dv))
-        linear.matmul(h, self.w_g, gate, linear.EPI_STORE, ctx)
+        gate = proj[:, 2 * H * dk + H * dv:]                       # the gate's arguments stay float32 sums
         rope = self.position.kernel_args(ctx.device)
         if rope.inv_freq:
             K.rotary_rows(proj, lay.pos_of, 2 * H, dk, rope, H, self.key_scale, ctx.stream)      # q heads, then k heads (scaled)
